@@ -1,0 +1,78 @@
+// Workspace shared by the two attention steps (prepare and forward).  The caller owns the memory;
+// this header only fixes where each array lives inside it.
+//
+//   q      [BH, Sq_pad, 128]   INT8 or fp16, softmax scale * log2(e) folded in (INT8: per-token scale)
+//   k      [BH, Sk_pad, 128]   INT8 or fp16, per-(batch, head, channel) sequence mean removed
+//   vt     [BH, 128, Sk_pad]   FP8 e4m3 or fp16, transposed so that tokens are contiguous
+//   q_scale[BH, Sq_pad]  k_scale[BH, Sk_pad/128]  v_scale[BH, 128]      fp32
+//   k_mean [BH, 128]           fp32
+//   part   [BH, chunks, 2, 128] fp32 partial column sums of K and column maxima of |V|
+// Sq_pad is Sq rounded up to 256 (one CTA of the forward kernel owns 256 query rows), Sk_pad is Sk
+// rounded up to 128; the prepare step zero-fills the padding.
+#pragma once
+#include "common.cuh"
+
+namespace dax {
+
+constexpr int64_t kStatChunk = 512;  // tokens per partial-statistics block
+
+struct AttnWorkspace {
+  void* q;
+  void* k;
+  void* vt;
+  float* q_scale;
+  float* k_scale;
+  float* v_scale;
+  float* k_mean;
+  float* part;
+  int64_t Sq_pad, Sk_pad, chunks;
+  size_t bytes;
+};
+
+inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
+
+// Fills `ws`; with base == nullptr only the size is computed.
+inline int attn_workspace_layout(int64_t B, int64_t heads, int64_t Sq, int64_t Sk, int mode, void* base,
+                                 size_t available, AttnWorkspace* ws) {
+  DAX_REQUIRE(B > 0 && heads > 0 && Sq > 0 && Sk > 0, DAX_ERR_INVALID, "attention: bad shape B=%lld heads=%lld Sq=%lld Sk=%lld",
+              (long long)B, (long long)heads, (long long)Sq, (long long)Sk);
+  DAX_REQUIRE(mode == DAX_ATTN_QK_I8_PV_F8 || mode == DAX_ATTN_QK_F16_PV_F16, DAX_ERR_UNSUPPORTED,
+              "attention: unknown mode %d", mode);
+  const int64_t BH = B * heads;
+  DAX_REQUIRE(BH <= 65535, DAX_ERR_UNSUPPORTED, "attention: batch*heads=%lld exceeds 65535", (long long)BH);
+  const int eq = mode == DAX_ATTN_QK_I8_PV_F8 ? 1 : 2;
+  ws->Sq_pad = round_up(Sq, 256);
+  ws->Sk_pad = round_up(Sk, 128);
+  ws->chunks = (Sk + kStatChunk - 1) / kStatChunk;
+  DAX_REQUIRE(BH * ws->Sq_pad < (1ll << 31) && BH * ws->Sk_pad < (1ll << 31), DAX_ERR_UNSUPPORTED,
+              "attention: batch*heads*sequence exceeds 2^31 rows");
+  size_t off = 0;
+  auto take = [&](size_t n) {
+    size_t o = off;
+    off += (n + 1023) / 1024 * 1024;
+    return o;
+  };
+  uint8_t* b = static_cast<uint8_t*>(base);
+  const size_t o_q = take(static_cast<size_t>(BH) * ws->Sq_pad * 128 * eq);
+  const size_t o_k = take(static_cast<size_t>(BH) * ws->Sk_pad * 128 * eq);
+  const size_t o_v = take(static_cast<size_t>(BH) * ws->Sk_pad * 128 * eq);
+  const size_t o_qs = take(static_cast<size_t>(BH) * ws->Sq_pad * 4);
+  const size_t o_ks = take(static_cast<size_t>(BH) * (ws->Sk_pad / 128) * 4);
+  const size_t o_vs = take(static_cast<size_t>(BH) * 128 * 4);
+  const size_t o_km = take(static_cast<size_t>(BH) * 128 * 4);
+  const size_t o_pt = take(static_cast<size_t>(BH) * ws->chunks * 2 * 128 * 4);
+  ws->bytes = off;
+  if (base != nullptr) {
+    DAX_REQUIRE((reinterpret_cast<uintptr_t>(base) & 1023u) == 0, DAX_ERR_ALIGN, "attention: workspace must be 1024-byte aligned");
+    DAX_REQUIRE(available >= off, DAX_ERR_INVALID, "attention: workspace of %zu bytes is smaller than the %zu required", available, off);
+    ws->q = b + o_q; ws->k = b + o_k; ws->vt = b + o_v;
+    ws->q_scale = reinterpret_cast<float*>(b + o_qs);
+    ws->k_scale = reinterpret_cast<float*>(b + o_ks);
+    ws->v_scale = reinterpret_cast<float*>(b + o_vs);
+    ws->k_mean = reinterpret_cast<float*>(b + o_km);
+    ws->part = reinterpret_cast<float*>(b + o_pt);
+  }
+  return DAX_OK;
+}
+
+}  // namespace dax

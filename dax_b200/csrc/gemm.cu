@@ -1,0 +1,345 @@
+// INT8 / FP8 GEMM with fused de-quantisation for the dynamic linears:
+//     out[t, n] = cast( (acc[t, n] * sx[t]) * sw[n] ) + bias[n],   acc = qx . qw^T
+//
+// Tensor-core bound (2*M*N*K operations on the 8-bit tcgen05 pipe).  One persistent CTA per SM,
+// warp-specialised:
+//   warp 0      TMA producer: 128x128-byte tiles of qx and 256x128-byte tiles of qw into a 4-stage
+//               shared-memory ring (128-byte swizzle, no multicast)
+//   warp 1      MMA issuer: tcgen05.mma kind::i8 / kind::f8f6f4, 128x256 accumulator in tensor memory,
+//               two accumulator buffers (2 x 256 columns) so the epilogue of tile i overlaps the
+//               main loop of tile i+1
+//   warps 2..5  epilogue: tcgen05.ld 32 columns at a time, de-quantise, add bias, round, optional
+//               per-row sum of squares, 16-byte stores
+// Tiles are visited column-block-fastest so that the CTAs of one wave share the same rows of qx
+// in L2 while the (much smaller) weight matrix stays L2-resident.
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace dax {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BKB = 128;  // bytes (= elements) of K per stage: one 128-byte swizzle row
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BKB;
+constexpr int B_BYTES = BN * BKB;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+struct GemmParams {
+  const float* sx;
+  const float* sw;
+  const void* bias;
+  void* out;
+  float* row_sumsq;
+  void* acc_dump;
+  int* status;
+  int64_t M, N, K, ldo, out_col_group, out_group_stride;
+  int m_tiles, n_tiles, k_blocks;
+  int bias_dtype, out_dtype;
+};
+
+__device__ __forceinline__ float load_as_float(const void* p, int dt, int64_t i) {
+  if (dt == DAX_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+  if (dt == DAX_F16) return __half2float(static_cast<const __half*>(p)[i]);
+  return static_cast<const float*>(p)[i];
+}
+
+__device__ __forceinline__ float round_to(float v, int dt) {
+  if (dt == DAX_BF16) return __bfloat162float(__float2bfloat16_rn(v));
+  if (dt == DAX_F16) return __half2float(__float2half_rn(v));
+  return v;
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_dequant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const GemmParams p, const uint32_t idesc) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full = bars;                  // [STAGES] TMA -> MMA
+  uint64_t* empty = bars + STAGES;        // [STAGES] MMA -> TMA
+  uint64_t* acc_full = bars + 2 * STAGES; // [2] MMA -> epilogue
+  uint64_t* acc_empty = acc_full + 2;     // [2] epilogue -> MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_tiles = p.m_tiles * p.n_tiles;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&map_a);
+      tma_prefetch_desc(&map_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const int m0 = (tile / p.n_tiles) * BM;
+        const int n0 = (tile % p.n_tiles) * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+          uint8_t* a_dst = smem + s * STAGE_BYTES;
+          uint8_t* b_dst = a_dst + A_BYTES;
+          mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+          tma_load_2d(a_dst, &map_a, &full[s], kb * BKB, m0);
+          tma_load_2d(b_dst, &map_b, &full[s], kb * BKB, n0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0;
+      uint32_t local_tile = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local_tile) {
+        const uint32_t buf = local_tile & 1u;
+        const uint32_t use = local_tile >> 1;  // how often this buffer has been used before
+        if (!mbar_wait(&acc_empty[buf], (use & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+          const uint64_t da = make_desc_k_sw128(a_addr);
+          const uint64_t db = make_desc_k_sw128(a_addr + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BKB / 32; ++k) {
+            // advancing K by 32 bytes inside the 128-byte swizzle row = +2 in the encoded address
+            umma_ss<KIND>(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
+        }
+        if (ok) umma_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32) belong to this warp
+    uint32_t local_tile = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local_tile) {
+      const uint32_t buf = local_tile & 1u;
+      const uint32_t use = local_tile >> 1;
+      const int n_blk = tile % p.n_tiles;
+      const int64_t m0 = static_cast<int64_t>(tile / p.n_tiles) * BM;
+      const int64_t n0 = static_cast<int64_t>(n_blk) * BN;
+      if (!mbar_wait(&acc_full[buf], use & 1u, abort_flag)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int64_t row = m0 + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      const float sx = row_ok ? p.sx[row] : 0.f;
+      float sumsq = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN + c * 32, r);
+        tmem_wait_ld();
+        const int64_t col0 = n0 + c * 32;
+        if (col0 >= p.N) continue;
+        if (p.acc_dump != nullptr && row_ok) {
+          uint32_t* dump = static_cast<uint32_t*>(p.acc_dump) + row * p.N + col0;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) dump[j] = r[j];
+        }
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int64_t col = col0 + j;
+          const bool col_ok = col < p.N;
+          const float sw = col_ok ? __ldg(p.sw + col) : 0.f;
+          float a;
+          if constexpr (KIND == KIND_I8) a = __int2float_rn(static_cast<int>(r[j]));
+          else a = __uint_as_float(r[j]);
+          float t = __fmul_rn(__fmul_rn(a, sx), sw);
+          if constexpr (KIND == KIND_I8) {
+            // reference order: cast to the output dtype, then add the bias in the output dtype
+            t = round_to(t, p.out_dtype);
+            if (p.bias != nullptr && col_ok) t = round_to(__fadd_rn(t, load_as_float(p.bias, p.bias_dtype, col)), p.out_dtype);
+          } else {
+            // scaled-matmul semantics: bias joins in fp32, one rounding
+            if (p.bias != nullptr && col_ok) t = __fadd_rn(t, load_as_float(p.bias, p.bias_dtype, col));
+            t = round_to(t, p.out_dtype);
+          }
+          v[j] = t;
+          sumsq = fmaf(t, t, sumsq);
+        }
+        if (row_ok) {
+          const int64_t g = col0 / p.out_col_group;
+          const int64_t off = g * p.out_group_stride + row * p.ldo + (col0 - g * p.out_col_group);
+          if (p.out_dtype == DAX_F32) {
+            float* o = static_cast<float*>(p.out) + off;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              if (col0 + j < p.N) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          } else {
+            uint16_t* o = static_cast<uint16_t*>(p.out) + off;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col0 + j < p.N) {
+                uint32_t w[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  uint16_t lo, hi;
+                  if (p.out_dtype == DAX_BF16) {
+                    lo = __bfloat16_as_ushort(__float2bfloat16_rn(v[j + 2 * q]));
+                    hi = __bfloat16_as_ushort(__float2bfloat16_rn(v[j + 2 * q + 1]));
+                  } else {
+                    lo = __half_as_ushort(__float2half_rn(v[j + 2 * q]));
+                    hi = __half_as_ushort(__float2half_rn(v[j + 2 * q + 1]));
+                  }
+                  w[q] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+                }
+                *reinterpret_cast<uint4*>(o + j) = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            }
+          }
+        }
+      }
+      // all TMEM reads of this buffer are complete (wait::ld above): hand it back to the MMA warp
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      if (p.row_sumsq != nullptr && row_ok) p.row_sumsq[row * p.n_tiles + n_blk] = sumsq;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, DAX_ERR_TIMEOUT);
+}
+
+bool is_f8(int dt) { return dt == DAX_E4M3 || dt == DAX_E5M2; }
+
+}  // namespace
+}  // namespace dax
+
+extern "C" int dax_gemm_dequant(const void* qx, int a_dtype, const float* sx, const void* qw, int b_dtype,
+                                const float* sw, const void* bias, int bias_dtype, void* out, int out_dtype,
+                                int64_t M, int64_t N, int64_t K, int64_t ldo, int64_t out_col_group,
+                                int64_t out_group_stride, float* row_sumsq, void* acc_dump, void* stream) {
+  using namespace dax;
+  DAX_REQUIRE(M >= 0 && N > 0 && K > 0, DAX_ERR_INVALID, "gemm_dequant: bad shape M=%lld N=%lld K=%lld",
+              (long long)M, (long long)N, (long long)K);
+  if (M == 0) return DAX_OK;
+  DAX_REQUIRE(qx && sx && qw && sw && out, DAX_ERR_INVALID, "gemm_dequant: null pointer");
+  const bool i8 = a_dtype == DAX_I8 && b_dtype == DAX_I8;
+  const bool f8 = is_f8(a_dtype) && is_f8(b_dtype);
+  DAX_REQUIRE(i8 || f8, DAX_ERR_UNSUPPORTED, "gemm_dequant: operand dtypes (%d, %d) must be both I8 or both FP8",
+              a_dtype, b_dtype);
+  DAX_REQUIRE(out_dtype == DAX_BF16 || out_dtype == DAX_F16 || out_dtype == DAX_F32, DAX_ERR_UNSUPPORTED,
+              "gemm_dequant: out_dtype %d is not BF16/F16/F32", out_dtype);
+  DAX_REQUIRE(bias == nullptr || bias_dtype == DAX_BF16 || bias_dtype == DAX_F16 || bias_dtype == DAX_F32,
+              DAX_ERR_UNSUPPORTED, "gemm_dequant: bias_dtype %d is not BF16/F16/F32", bias_dtype);
+  DAX_REQUIRE(K % 16 == 0, DAX_ERR_ALIGN, "gemm_dequant: K=%lld must be a multiple of 16", (long long)K);
+  DAX_REQUIRE(N % 8 == 0, DAX_ERR_ALIGN, "gemm_dequant: N=%lld must be a multiple of 8", (long long)N);
+  DAX_REQUIRE(out_col_group > 0 && N % out_col_group == 0 && (out_col_group == N || out_col_group % 32 == 0),
+              DAX_ERR_ALIGN, "gemm_dequant: out_col_group=%lld must divide N and be a multiple of 32",
+              (long long)out_col_group);
+  DAX_REQUIRE(ldo % 8 == 0 && out_group_stride % 8 == 0, DAX_ERR_ALIGN,
+              "gemm_dequant: ldo and out_group_stride must be multiples of 8 elements");
+  DAX_REQUIRE(aligned16(qx) && aligned16(qw) && aligned16(out), DAX_ERR_ALIGN,
+              "gemm_dequant: qx, qw and out must be 16-byte aligned");
+  DAX_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), DAX_ERR_UNSUPPORTED, "gemm_dequant: size overflow");
+
+  CUtensorMap map_a, map_b;
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+    uint64_t strides[2] = {1, static_cast<uint64_t>(K)};
+    uint32_t box[2] = {BKB, BM};
+    int rc = make_tma_map(&map_a, qx, 1, 2, dims, strides, box);
+    if (rc != DAX_OK) return rc;
+  }
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+    uint64_t strides[2] = {1, static_cast<uint64_t>(K)};
+    uint32_t box[2] = {BKB, BN};
+    int rc = make_tma_map(&map_b, qw, 1, 2, dims, strides, box);
+    if (rc != DAX_OK) return rc;
+  }
+
+  GemmParams p;
+  p.sx = sx; p.sw = sw; p.bias = bias; p.out = out; p.row_sumsq = row_sumsq; p.acc_dump = acc_dump;
+  p.status = device_status_ptr();
+  DAX_REQUIRE(p.status != nullptr, DAX_ERR_CUDA, "gemm_dequant: cannot resolve the device status word");
+  p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.out_col_group = out_col_group; p.out_group_stride = out_group_stride;
+  p.m_tiles = static_cast<int>((M + BM - 1) / BM);
+  p.n_tiles = static_cast<int>((N + BN - 1) / BN);
+  p.k_blocks = static_cast<int>((K + BKB - 1) / BKB);
+  p.bias_dtype = bias_dtype; p.out_dtype = out_dtype;
+  const int64_t total = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
+  DAX_REQUIRE(total < (1ll << 31), DAX_ERR_UNSUPPORTED, "gemm_dequant: too many tiles");
+  const int grid = static_cast<int>(total < sm_count() ? total : sm_count());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  if (i8) {
+    static bool attr_done = false;
+    if (!attr_done) {
+      DAX_CUDA(cudaFuncSetAttribute(gemm_dequant_kernel<KIND_I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+      attr_done = true;
+    }
+    const uint32_t idesc = make_idesc(/*c=s32*/ 2, /*a=s8*/ 1, /*b=s8*/ 1, BM, BN);
+    gemm_dequant_kernel<KIND_I8><<<grid, GEMM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p, idesc);
+  } else {
+    static bool attr_done = false;
+    if (!attr_done) {
+      DAX_CUDA(cudaFuncSetAttribute(gemm_dequant_kernel<KIND_F8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+      attr_done = true;
+    }
+    const uint32_t idesc = make_idesc(/*c=f32*/ 1, a_dtype == DAX_E5M2 ? 1 : 0, b_dtype == DAX_E5M2 ? 1 : 0, BM, BN);
+    gemm_dequant_kernel<KIND_F8><<<grid, GEMM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p, idesc);
+  }
+  DAX_CUDA(cudaGetLastError());
+  return DAX_OK;
+}
+
+extern "C" int dax_gemm_i8_dequant(const void* qx, const float* sx, const void* qw, const float* sw, const void* bias,
+                                   int bias_dtype, void* out, int out_dtype, int64_t M, int64_t N, int64_t K,
+                                   int64_t ldo, float* row_sumsq, int32_t* acc_dump, void* stream) {
+  return dax_gemm_dequant(qx, DAX_I8, sx, qw, DAX_I8, sw, bias, bias_dtype, out, out_dtype, M, N, K, ldo, N, 0,
+                          row_sumsq, acc_dump, stream);
+}
+
+extern "C" int dax_gemm_f8_dequant(const void* qx, int a_dtype, const float* sx, const void* qw, const float* sw,
+                                   const void* bias, int bias_dtype, void* out, int out_dtype, int64_t M, int64_t N,
+                                   int64_t K, int64_t ldo, float* row_sumsq, float* acc_dump, void* stream) {
+  return dax_gemm_dequant(qx, a_dtype, sx, qw, DAX_E4M3, sw, bias, bias_dtype, out, out_dtype, M, N, K, ldo, N, 0,
+                          row_sumsq, acc_dump, stream);
+}

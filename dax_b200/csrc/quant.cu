@@ -1,0 +1,209 @@
+// Per-token dynamic activation quantiser (absmax -> scale -> INT8 / FP8), one pass over HBM.
+//
+// HBM-bound: 2 (or 4) bytes read and 1 byte written per element plus 4 bytes per row.  A row is
+// read once with 128-bit loads into registers, reduced, and quantised from registers.  Rows are
+// mapped to a warp (short rows) or to a whole CTA (long rows) so that every thread has work.
+//
+// Arithmetic follows the reference bit for bit (dax/quant/nn/dynamic/functional.py:124-135 and
+// dax/quant/nn/quantized/functional.py:11-20, evaluated eagerly):
+//   amax  = max |x|                       (exact in any precision)
+//   scale = round_to_input_dtype(amax / qmax), floored at fp32 eps, widened to fp32
+//   INT8: q = clamp(rint(x * (1.0f / scale)), -128, 127)    (multiply by the reciprocal)
+//   FP8 : q = round_nearest_even_to_fp8(clamp(x / scale))   (true division)
+// All fp32 operations are the IEEE round-to-nearest intrinsics so that the compiler cannot
+// contract or approximate them.
+#include "common.cuh"
+
+namespace dax {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kMaxVec = 8;  // 16-byte vectors cached per thread
+
+template <typename T> struct VecTraits;
+template <> struct VecTraits<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  __device__ static float round_trip(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
+};
+template <> struct VecTraits<__half> {
+  static constexpr int N = 8;
+  __device__ static float to_f(__half v) { return __half2float(v); }
+  __device__ static float round_trip(float f) { return __half2float(__float2half_rn(f)); }
+};
+template <> struct VecTraits<float> {
+  static constexpr int N = 4;
+  __device__ static float to_f(float v) { return v; }
+  __device__ static float round_trip(float f) { return f; }
+};
+
+template <typename T>
+struct alignas(16) Vec {
+  T v[VecTraits<T>::N];
+};
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+template <int QDT>
+__device__ __forceinline__ uint8_t quant_one(float x, float scale, float inv_scale) {
+  if constexpr (QDT == DAX_I8) {
+    float r = rintf(__fmul_rn(x, inv_scale));
+    r = fminf(fmaxf(r, -128.f), 127.f);
+    return static_cast<uint8_t>(static_cast<int8_t>(static_cast<int>(r)));
+  } else if constexpr (QDT == DAX_E4M3) {
+    float r = __fdiv_rn(x, scale);
+    r = fminf(fmaxf(r, -448.f), 448.f);
+    return static_cast<uint8_t>(__nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E4M3));
+  } else {
+    float r = __fdiv_rn(x, scale);
+    r = fminf(fmaxf(r, -57344.f), 57344.f);
+    return static_cast<uint8_t>(__nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E5M2));
+  }
+}
+
+// TPR threads cooperate on one row; a CTA of kThreads handles kThreads / TPR rows.
+template <typename T, int QDT, int TPR>
+__global__ void __launch_bounds__(kThreads)
+quant_rowwise_kernel(const T* __restrict__ x, int64_t M, int64_t K, int64_t ldx, int64_t col_group,
+                     int64_t group_stride, uint8_t* __restrict__ q, float* __restrict__ scale) {
+  constexpr int N = VecTraits<T>::N;
+  constexpr int RPB = kThreads / TPR;
+  constexpr float qmax = QDT == DAX_I8 ? 127.f : (QDT == DAX_E4M3 ? 448.f : 57344.f);
+  __shared__ float red[kThreads / 32];
+
+  const int tid = threadIdx.x;
+  const int sub = tid % TPR;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * RPB + tid / TPR;
+  const bool live = row < M;
+  const int64_t nvec = K / N;
+  const bool cached = nvec <= static_cast<int64_t>(TPR) * kMaxVec;
+
+  Vec<T> regs[kMaxVec];
+  float amax = 0.f;
+  auto src = [&](int64_t vi) -> const Vec<T>* {
+    const int64_t n = vi * N;
+    const int64_t g = n / col_group;
+    return reinterpret_cast<const Vec<T>*>(x + g * group_stride + row * ldx + (n - g * col_group));
+  };
+  if (live) {
+    if (cached) {
+#pragma unroll
+      for (int i = 0; i < kMaxVec; ++i) {
+        const int64_t vi = sub + static_cast<int64_t>(i) * TPR;
+        if (vi < nvec) {
+          regs[i] = *src(vi);
+#pragma unroll
+          for (int j = 0; j < N; ++j) amax = fmaxf(amax, fabsf(VecTraits<T>::to_f(regs[i].v[j])));
+        }
+      }
+    } else {
+      for (int64_t vi = sub; vi < nvec; vi += TPR) {
+        Vec<T> t = *src(vi);
+#pragma unroll
+        for (int j = 0; j < N; ++j) amax = fmaxf(amax, fabsf(VecTraits<T>::to_f(t.v[j])));
+      }
+    }
+  }
+  amax = warp_max(amax);
+  if constexpr (TPR > 32) {
+    if ((tid & 31) == 0) red[tid >> 5] = amax;
+    __syncthreads();
+    amax = red[0];
+#pragma unroll
+    for (int w = 1; w < kThreads / 32; ++w) amax = fmaxf(amax, red[w]);
+  }
+  if (!live) return;
+
+  float s = VecTraits<T>::round_trip(__fdiv_rn(amax, qmax));
+  s = fmaxf(s, 1.1920928955078125e-07f);
+  const float inv = __fdiv_rn(1.0f, s);
+  if (sub == 0) scale[row] = s;
+
+  uint8_t* qrow = q + row * K;
+  auto emit = [&](const Vec<T>& t, int64_t vi) {
+    if constexpr (N == 8) {
+      uint2 o;
+      uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        w0 |= static_cast<uint32_t>(quant_one<QDT>(VecTraits<T>::to_f(t.v[j]), s, inv)) << (8 * j);
+        w1 |= static_cast<uint32_t>(quant_one<QDT>(VecTraits<T>::to_f(t.v[4 + j]), s, inv)) << (8 * j);
+      }
+      o.x = w0;
+      o.y = w1;
+      *reinterpret_cast<uint2*>(qrow + vi * 8) = o;
+    } else {
+      uint32_t w0 = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        w0 |= static_cast<uint32_t>(quant_one<QDT>(VecTraits<T>::to_f(t.v[j]), s, inv)) << (8 * j);
+      *reinterpret_cast<uint32_t*>(qrow + vi * 4) = w0;
+    }
+  };
+  if (cached) {
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+      const int64_t vi = sub + static_cast<int64_t>(i) * TPR;
+      if (vi < nvec) emit(regs[i], vi);
+    }
+  } else {
+    for (int64_t vi = sub; vi < nvec; vi += TPR) emit(*src(vi), vi);
+  }
+}
+
+template <typename T, int QDT>
+int launch(const void* x, int64_t M, int64_t K, int64_t ldx, int64_t col_group, int64_t group_stride, void* q,
+           float* scale, cudaStream_t st) {
+  const int64_t nvec = K / VecTraits<T>::N;
+  if (nvec <= 32 * kMaxVec) {
+    constexpr int RPB = kThreads / 32;
+    const int64_t blocks = (M + RPB - 1) / RPB;
+    quant_rowwise_kernel<T, QDT, 32><<<static_cast<unsigned>(blocks), kThreads, 0, st>>>(
+        static_cast<const T*>(x), M, K, ldx, col_group, group_stride, static_cast<uint8_t*>(q), scale);
+  } else {
+    quant_rowwise_kernel<T, QDT, kThreads><<<static_cast<unsigned>(M), kThreads, 0, st>>>(
+        static_cast<const T*>(x), M, K, ldx, col_group, group_stride, static_cast<uint8_t*>(q), scale);
+  }
+  DAX_CUDA(cudaGetLastError());
+  return DAX_OK;
+}
+
+template <typename T>
+int dispatch_q(int q_dtype, const void* x, int64_t M, int64_t K, int64_t ldx, int64_t col_group,
+               int64_t group_stride, void* q, float* scale, cudaStream_t st) {
+  switch (q_dtype) {
+    case DAX_I8: return launch<T, DAX_I8>(x, M, K, ldx, col_group, group_stride, q, scale, st);
+    case DAX_E4M3: return launch<T, DAX_E4M3>(x, M, K, ldx, col_group, group_stride, q, scale, st);
+    case DAX_E5M2: return launch<T, DAX_E5M2>(x, M, K, ldx, col_group, group_stride, q, scale, st);
+    default: return fail(DAX_ERR_UNSUPPORTED, "quant_rowwise: q_dtype %d is not I8/E4M3/E5M2", q_dtype);
+  }
+}
+
+}  // namespace
+}  // namespace dax
+
+extern "C" int dax_quant_rowwise(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, int64_t col_group,
+                                 int64_t group_stride, void* q, int q_dtype, float* scale, void* stream) {
+  using namespace dax;
+  DAX_REQUIRE(M >= 0 && K > 0, DAX_ERR_INVALID, "quant_rowwise: bad shape M=%lld K=%lld", (long long)M, (long long)K);
+  if (M == 0) return DAX_OK;
+  DAX_REQUIRE(x && q && scale, DAX_ERR_INVALID, "quant_rowwise: null pointer");
+  DAX_REQUIRE(M < (1ll << 31), DAX_ERR_UNSUPPORTED, "quant_rowwise: M=%lld too large", (long long)M);
+  DAX_REQUIRE(K % 16 == 0, DAX_ERR_ALIGN, "quant_rowwise: K=%lld must be a multiple of 16", (long long)K);
+  DAX_REQUIRE(col_group > 0 && col_group % 16 == 0 && K % col_group == 0, DAX_ERR_ALIGN,
+              "quant_rowwise: col_group=%lld must be a multiple of 16 that divides K", (long long)col_group);
+  DAX_REQUIRE(ldx % 8 == 0 && group_stride % 8 == 0, DAX_ERR_ALIGN,
+              "quant_rowwise: ldx and group_stride must be multiples of 8 elements");
+  DAX_REQUIRE(aligned16(x) && aligned16(q), DAX_ERR_ALIGN, "quant_rowwise: x and q must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (x_dtype) {
+    case DAX_BF16: return dispatch_q<__nv_bfloat16>(q_dtype, x, M, K, ldx, col_group, group_stride, q, scale, st);
+    case DAX_F16: return dispatch_q<__half>(q_dtype, x, M, K, ldx, col_group, group_stride, q, scale, st);
+    case DAX_F32: return dispatch_q<float>(q_dtype, x, M, K, ldx, col_group, group_stride, q, scale, st);
+    default: return fail(DAX_ERR_UNSUPPORTED, "quant_rowwise: x_dtype %d is not BF16/F16/F32", x_dtype);
+  }
+}

@@ -1,0 +1,178 @@
+"""Tensor-level wrappers over the C ABI: one function per kernel family.
+
+These take CUDA ``torch.Tensor`` arguments, validate device/dtype/contiguity, allocate outputs with
+torch (the library itself never allocates) and enqueue on the current CUDA stream.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import I64x3, check, load
+
+_DT = {torch.bfloat16: _lib.DAX_BF16, torch.float16: _lib.DAX_F16, torch.float32: _lib.DAX_F32,
+       torch.int8: _lib.DAX_I8, torch.float8_e4m3fn: _lib.DAX_E4M3, torch.float8_e5m2: _lib.DAX_E5M2}
+
+ATTN_MODES = {"sage": _lib.DAX_ATTN_QK_I8_PV_F8, "int8_fp8": _lib.DAX_ATTN_QK_I8_PV_F8,
+              "f16": _lib.DAX_ATTN_QK_F16_PV_F16}
+
+
+def _dt(dtype: torch.dtype) -> int:
+    if dtype not in _DT:
+        raise NotImplementedError(f"dax_b200: dtype {dtype} is not supported")
+    return _DT[dtype]
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*ts) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("dax_b200 operators run on CUDA tensors only; there is no CPU path")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def quant_rowwise(x: torch.Tensor, q_dtype: torch.dtype, *, col_group: Optional[int] = None,
+                  group_stride: int = 0, rows: Optional[int] = None, cols: Optional[int] = None,
+                  ldx: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-token quantisation of a ``[M, K]`` matrix -> ``(q [M, K], scale [M, 1] fp32)``.
+
+    With ``col_group``/``group_stride`` (and explicit ``rows``, ``cols``, ``ldx``) ``x`` is read as
+    column groups living in separate slabs, see ``dax_quant_rowwise`` in ``include/dax_b200.h``."""
+    _need_cuda(x)
+    if col_group is None:
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        M, K = x2.shape
+        ld, cg, gs = x2.stride(0) if M > 1 else K, K, 0
+        src = x2
+    else:
+        M, K, ld, cg, gs, src = rows, cols, ldx, col_group, group_stride, x
+    q = torch.empty((M, K), dtype=q_dtype, device=x.device)
+    scale = torch.empty((M, 1), dtype=torch.float32, device=x.device)
+    check(load().dax_quant_rowwise(src.data_ptr(), _dt(x.dtype), M, K, ld, cg, gs, q.data_ptr(), _dt(q_dtype),
+                                   scale.data_ptr(), _stream()))
+    return q, scale
+
+
+def gemm_dequant(qx: torch.Tensor, sx: torch.Tensor, qw: torch.Tensor, sw: torch.Tensor,
+                 bias: Optional[torch.Tensor], out_dtype: torch.dtype, *, out: Optional[torch.Tensor] = None,
+                 ldo: Optional[int] = None, out_col_group: Optional[int] = None, out_group_stride: int = 0,
+                 row_sumsq: Optional[torch.Tensor] = None, acc_dump: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out = cast((acc(qx @ qw.T) * sx) * sw) + bias`` on the tcgen05 INT8 / FP8 pipe."""
+    _need_cuda(qx, sx, qw, sw, bias, out)
+    M, K = qx.shape
+    N = qw.shape[0]
+    assert qw.shape[1] == K and qx.is_contiguous() and qw.is_contiguous()
+    assert sx.numel() == M and sw.numel() == N and sx.dtype == torch.float32 and sw.dtype == torch.float32
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=qx.device)
+        ldo = N
+    if out_col_group is None:
+        out_col_group = N
+    check(load().dax_gemm_dequant(qx.data_ptr(), _dt(qx.dtype), sx.data_ptr(), qw.data_ptr(), _dt(qw.dtype),
+                                  sw.data_ptr(), _ptr(bias), _dt(bias.dtype) if bias is not None else 0,
+                                  out.data_ptr(), _dt(out_dtype), M, N, K, ldo, out_col_group, out_group_stride,
+                                  _ptr(row_sumsq), _ptr(acc_dump), _stream()))
+    return out
+
+
+def rmsnorm_rope_pack(x: torch.Tensor, *, norm_weight: Optional[torch.Tensor], do_norm: bool, eps: float = 1e-6,
+                      rope_cos: Optional[torch.Tensor] = None, rope_sin: Optional[torch.Tensor] = None,
+                      token_offset: int = 0, row_sumsq: Optional[torch.Tensor] = None,
+                      out: Optional[torch.Tensor] = None, ldo: Optional[int] = None,
+                      col_group: Optional[int] = None, group_stride: int = 0) -> torch.Tensor:
+    """RMSNorm over the full row + rotary embedding + write into a (possibly grouped) layout."""
+    _need_cuda(x, norm_weight, rope_cos, rope_sin, row_sumsq, out)
+    s, D = x.shape
+    assert x.stride(1) == 1
+    if out is None:
+        out = torch.empty((s, D), dtype=x.dtype, device=x.device)
+        ldo = D
+    if col_group is None:
+        col_group = D
+    n_part = row_sumsq.shape[1] if row_sumsq is not None else 0
+    check(load().dax_rmsnorm_rope_pack(x.data_ptr(), _dt(x.dtype), s, D, x.stride(0), _ptr(row_sumsq), n_part,
+                                       1 if do_norm else 0, _ptr(norm_weight), float(eps), _ptr(rope_cos),
+                                       _ptr(rope_sin), token_offset, out.data_ptr(), ldo, col_group, group_stride,
+                                       _stream()))
+    return out
+
+
+def _bhsd_strides(t: torch.Tensor) -> I64x3:
+    assert t.dim() == 4 and t.shape[-1] == 128 and t.stride(-1) == 1, "expected [B, heads, S, 128], channels contiguous"
+    return I64x3(t.stride(0), t.stride(1), t.stride(2))
+
+
+class AttentionPlan:
+    """Prepared operands of one attention call (workspace owned by torch)."""
+
+    def __init__(self, B, heads, Sq, Sk, mode, workspace, dtype):
+        self.B, self.heads, self.Sq, self.Sk, self.mode, self.workspace, self.dtype = B, heads, Sq, Sk, mode, workspace, dtype
+
+
+_WS_CACHE = {}
+
+
+def attn_workspace(B: int, heads: int, Sq: int, Sk: int, mode: int, device) -> torch.Tensor:
+    n = load().dax_attn_workspace_bytes(B, heads, Sq, Sk, mode)
+    if n == 0:
+        check(_lib.DAX_ERR_INVALID)
+    key = (str(device), n)
+    ws = _WS_CACHE.get(key)
+    if ws is None:
+        _WS_CACHE.clear()
+        ws = torch.empty(n + 1024, dtype=torch.uint8, device=device)
+        _WS_CACHE[key] = ws
+    off = (-ws.data_ptr()) % 1024
+    return ws[off:off + n]
+
+
+def attn_prepare(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mode: str = "sage",
+                 sm_scale: Optional[float] = None) -> AttentionPlan:
+    """q, k, v: ``[B, heads, S, 128]`` views (any batch/head/token strides) of bf16 or fp16."""
+    _need_cuda(q, k, v)
+    B, heads, Sq, d = q.shape
+    Sk = k.shape[2]
+    assert d == 128 and k.shape == v.shape and k.shape[:2] == q.shape[:2] and q.dtype == k.dtype == v.dtype
+    m = ATTN_MODES[mode]
+    ws = attn_workspace(B, heads, Sq, Sk, m, q.device)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(d)
+    check(load().dax_attn_prepare(q.data_ptr(), k.data_ptr(), v.data_ptr(), _dt(q.dtype), B, heads, Sq, Sk,
+                                  _bhsd_strides(q), _bhsd_strides(k), _bhsd_strides(v), float(sm_scale), m,
+                                  ws.data_ptr(), ws.numel(), _stream()))
+    return AttentionPlan(B, heads, Sq, Sk, m, ws, q.dtype)
+
+
+def attn_forward(plan: AttentionPlan, out: torch.Tensor, q_begin: int = 0, q_end: Optional[int] = None) -> torch.Tensor:
+    """Run the flash pass for queries ``[q_begin, q_end)`` into ``out`` (a ``[B, heads, Sq, 128]`` view)."""
+    _need_cuda(out)
+    if q_end is None:
+        q_end = plan.Sq
+    assert out.shape == (plan.B, plan.heads, plan.Sq, 128) and out.dtype == plan.dtype
+    check(load().dax_attn_forward(out.data_ptr(), _dt(out.dtype), plan.B, plan.heads, plan.Sq, plan.Sk,
+                                  _bhsd_strides(out), q_begin, q_end, plan.mode, plan.workspace.data_ptr(),
+                                  plan.workspace.numel(), _stream()))
+    return out
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mode: str = "sage",
+              sm_scale: Optional[float] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Non-causal attention over ``[B, heads, S, 128]``; the result has the memory layout
+    ``[B, S, heads, 128]`` (token-major, as the head->sequence exchange wants it) viewed as
+    ``[B, heads, S, 128]``."""
+    plan = attn_prepare(q, k, v, mode, sm_scale)
+    if out is None:
+        B, heads, Sq, d = q.shape
+        out = torch.empty((B, Sq, heads, d), dtype=q.dtype, device=q.device).transpose(1, 2)
+    return attn_forward(plan, out)

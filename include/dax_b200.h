@@ -1,0 +1,155 @@
+/*
+ * dax_b200 — C ABI of the B200 (sm_100a) kernels behind DAX's Ulysses self-attention hot path.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless the comment says "host".  The library never
+ *     allocates or frees device memory and keeps no pointer after a call returns (the one
+ *     documented exception owns a fixed file-scope buffer instead of allocating).
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it, nothing synchronises.
+ *   - Every function returns a dax_status; dax_last_error() gives the message of the calling
+ *     thread's last failure.  Shape / alignment / dtype problems are reported BEFORE any launch.
+ *   - A kernel whose bounded device-side wait ran out raises the device status word, readable
+ *     with dax_device_status() (that call synchronises).
+ *   - Reference locations are given as path:line inside the RiseAI-Sys/DAX project.
+ */
+#ifndef DAX_B200_H_
+#define DAX_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  DAX_OK = 0,
+  DAX_ERR_INVALID = 1,     /* bad shape / null pointer / inconsistent arguments            */
+  DAX_ERR_ALIGN = 2,       /* pointer or leading dimension not aligned as documented        */
+  DAX_ERR_UNSUPPORTED = 3, /* dtype combination or size outside what the kernels implement  */
+  DAX_ERR_CUDA = 4,        /* a CUDA runtime / driver call failed                           */
+  DAX_ERR_TIMEOUT = 5      /* device status: a bounded wait inside a kernel ran out         */
+} dax_status;
+
+typedef enum {
+  DAX_BF16 = 0,
+  DAX_F16 = 1,
+  DAX_F32 = 2,
+  DAX_I8 = 3,
+  DAX_E4M3 = 4, /* float8_e4m3fn */
+  DAX_E5M2 = 5
+} dax_dtype;
+
+/* Precision of the two tensor-core contractions of the attention kernel. */
+typedef enum {
+  DAX_ATTN_QK_I8_PV_F8 = 0,  /* INT8 Q.K^T, FP8(e4m3) P.V  — the SageAttention2-style mode   */
+  DAX_ATTN_QK_F16_PV_F16 = 1 /* fp16 Q.K^T, fp16 P.V       — high-accuracy mode              */
+} dax_attn_mode;
+
+int dax_version(void);
+const char* dax_last_error(void);
+
+/* Reads (and clears) the device status word of the current device: DAX_OK or DAX_ERR_TIMEOUT.
+ * Synchronises the device.  `host_status` is a host pointer. */
+int dax_device_status(int* host_status);
+
+/* ---------------------------------------------------------------------------------------------
+ * Per-token dynamic activation quantiser.
+ * Replaces dax/quant/nn/dynamic/functional.py:54-148 (_dynamic_quantize_func, per_token_symmetric)
+ * with dax/quant/nn/quantized/functional.py:11-20 (quantize_to_fp8 / quantize_to_int8).
+ *
+ * x is a logical [M, K] matrix of x_dtype (BF16 / F16 / F32).  Element (t, n) lives at
+ *     x + (n / col_group) * group_stride + t * ldx + (n % col_group)        (in elements)
+ * so that a matrix whose column groups sit in separate slabs (the receive buffer of the
+ * head->sequence exchange, [P, s, h*d]) is read in place; pass col_group = K, group_stride = 0
+ * for a plain row-major matrix.  q is [M, K] row-major of q_dtype (I8 / E4M3 / E5M2), scale is
+ * [M] fp32.  Bit-exact with the reference: absmax and absmax/qmax in the input dtype, floor at
+ * fp32 eps, INT8 = clamp(rint(x * (1/scale))), FP8 = round-to-nearest-even(x / scale).
+ * K and col_group must be multiples of 16; x, q 16-byte aligned; ldx, group_stride multiples of 8.
+ * ------------------------------------------------------------------------------------------- */
+int dax_quant_rowwise(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, int64_t col_group,
+                      int64_t group_stride, void* q, int q_dtype, float* scale, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Quantised GEMM with fused de-quantisation:  out = cast((acc(qx . qw^T) * sx) * sw) + bias.
+ * INT8 replaces dax/quant/nn/dynamic/linear.py:218-228 (int32 aten.mm, two fp32 scale multiplies
+ * in that order, cast to the output dtype, bias added in the output dtype) — bit-exact.
+ * FP8 replaces dax/quant/nn/dynamic/linear.py:155-173 (torch._scaled_mm, row-wise scales, fp32
+ * accumulation, bias inside, one rounding to the output dtype).
+ *
+ *   qx [M, K] row-major, a_dtype I8 | E4M3 | E5M2      sx [M] fp32
+ *   qw [N, K] row-major, b_dtype I8 | E4M3 | E5M2      sw [N] fp32
+ *   bias [N] of bias_dtype (BF16/F16/F32) or NULL
+ *   out: element (t, n) at out + (n / out_col_group) * out_group_stride + t * ldo + (n % out_col_group)
+ *        of out_dtype (BF16/F16/F32); out_col_group = N, out_group_stride = 0 for a plain matrix.
+ *        With out_col_group = h*d and out_group_stride = s*h*d the projection writes straight into
+ *        the send buffer [P, s, h, d] of the sequence->head exchange
+ *        (dax/parallel/patches/wanx2_1_t2v_opt/layer.py:35-42,113-120).
+ *   row_sumsq: optional [M, ceil(N/256)] fp32; slot (t, j) receives the sum of squares of the
+ *        rounded outputs of row t in column tile j (feeds the RMSNorm that follows a Q/K projection).
+ *   acc_dump: optional [M, N] int32 (INT8) / fp32 (FP8) raw accumulators, for parity tests.
+ * K % 16 == 0, N % 8 == 0, out_col_group % 32 == 0 (or == N), pointers 16-byte aligned.
+ * The reference's float fallback for M <= 16 (linear.py:186-202) does not exist here.
+ * ------------------------------------------------------------------------------------------- */
+int dax_gemm_dequant(const void* qx, int a_dtype, const float* sx, const void* qw, int b_dtype,
+                     const float* sw, const void* bias, int bias_dtype, void* out, int out_dtype, int64_t M,
+                     int64_t N, int64_t K, int64_t ldo, int64_t out_col_group, int64_t out_group_stride,
+                     float* row_sumsq, void* acc_dump, void* stream);
+
+/* Same kernel under the two names a binding would look for. */
+int dax_gemm_i8_dequant(const void* qx, const float* sx, const void* qw, const float* sw, const void* bias,
+                        int bias_dtype, void* out, int out_dtype, int64_t M, int64_t N, int64_t K,
+                        int64_t ldo, float* row_sumsq, int32_t* acc_dump, void* stream);
+int dax_gemm_f8_dequant(const void* qx, int a_dtype, const float* sx, const void* qw, const float* sw,
+                        const void* bias, int bias_dtype, void* out, int out_dtype, int64_t M, int64_t N,
+                        int64_t K, int64_t ldo, float* row_sumsq, float* acc_dump, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * RMSNorm over the full hidden dimension + 3-D rotary embedding + pack into the exchange layout.
+ * Replaces the norm_q / norm_k call sites (dax/adapters/wan/attn_adapter.py:82-85,108-109,121-122),
+ * apply_rotary_emb (attn_adapter.py:164-173; the reference rotates after the exchange, which is
+ * the same per-token, per-head operation) and the pack copy of the exchange
+ * (dax/parallel/patches/wanx2_1_t2v_opt/layer.py:113-120).
+ *
+ *   x [s, D] row-major (ldx), dtype BF16/F16; D = heads * 128.
+ *   row_sumsq: NULL (the kernel reduces each row itself) or [s, n_partials] fp32 partial sums of
+ *              squares written by dax_gemm_dequant; norm_weight [D] of x's dtype or NULL (no norm:
+ *              pass NULL weight and do_norm = 0).
+ *   rope_cos, rope_sin: [S_total, 64] fp32 tables (row = global token index), or NULL for no
+ *              rotation; token_offset = global index of local token 0.
+ *   out: element (t, n) at out + (n / col_group) * group_stride + t * ldo + (n % col_group).
+ * ------------------------------------------------------------------------------------------- */
+int dax_rmsnorm_rope_pack(const void* x, int dtype, int64_t s, int64_t D, int64_t ldx, const float* row_sumsq,
+                          int64_t n_partials, int do_norm, const void* norm_weight, float eps,
+                          const float* rope_cos, const float* rope_sin, int64_t token_offset, void* out,
+                          int64_t ldo, int64_t col_group, int64_t group_stride, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Quantised non-causal attention (replaces the attention dispatch at
+ * dax/adapters/wan/attn_adapter.py:198-229, i.e. sageattn_qk_int8_pv_fp8_cuda_sm90 / SDPA).
+ *
+ * q, k, v, o: [B, heads, S, 128] addressed by element strides (batch, head, token); the last
+ * dimension is contiguous; dtype BF16 or F16.  Sq may differ from Sk.
+ * Two steps share a caller-provided workspace (dax_attn_workspace_bytes):
+ *   dax_attn_prepare   K: per-(batch, head, channel) mean over the sequence removed, then INT8 per
+ *                      block of 128 tokens (or fp16); Q: softmax scale folded in, INT8 per token (or
+ *                      fp16); V: FP8 e4m3 with a per-channel scale, stored transposed (or fp16).
+ *   dax_attn_forward   flash-style pass over the prepared operands; may be called for any token
+ *                      range [q_begin, q_end) of the queries (the O-path micro-batches call it once
+ *                      per range), q_begin a multiple of 256.
+ * sm_scale: softmax scale (1/sqrt(128) in the reference).
+ * ------------------------------------------------------------------------------------------- */
+size_t dax_attn_workspace_bytes(int64_t B, int64_t heads, int64_t Sq, int64_t Sk, int mode);
+
+int dax_attn_prepare(const void* q, const void* k, const void* v, int dtype, int64_t B, int64_t heads,
+                     int64_t Sq, int64_t Sk, int64_t q_strides[3], int64_t k_strides[3], int64_t v_strides[3],
+                     float sm_scale, int mode, void* workspace, size_t workspace_bytes, void* stream);
+
+int dax_attn_forward(void* o, int dtype, int64_t B, int64_t heads, int64_t Sq, int64_t Sk, int64_t o_strides[3],
+                     int64_t q_begin, int64_t q_end, int mode, void* workspace, size_t workspace_bytes,
+                     void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DAX_B200_H_ */
