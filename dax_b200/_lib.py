@@ -38,7 +38,7 @@ SIGNATURES = {
     "dax_attn_prepare": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, I64x3,
                                  I64x3, I64x3, c_float, c_int, c_void_p, c_size_t, c_void_p]),
     "dax_attn_forward": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, I64x3, c_int64, c_int64,
-                                 c_int, c_void_p, c_size_t, c_void_p]),
+                                 c_int64, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
 }
 
 _LIB = None

@@ -1,0 +1,314 @@
+"""Attention processor for Wan2.1-style DiT blocks: the per-layer hot path.
+
+``DAXWanAttnProcessor2_0`` keeps the plugin protocol of the reference's processor
+(``dax/adapters/wan/attn_adapter.py:53-69``): it is installed with ``Attention.set_processor`` and
+called as ``processor(attn, hidden_states, encoder_hidden_states=None, attention_mask=None,
+rotary_emb=None)``.  What runs underneath is different.  Installing the processor IS the backend
+choice (there is no ``ATTENTION_BACKEND`` dispatch): every step is a kernel of ``libdax_b200``:
+
+  hidden_states [s, D]
+    -> per-token quantiser (once for Q, K and V)                           dax_quant_rowwise
+    -> INT8/FP8 GEMM + de-quantisation (+ per-row sum of squares)          dax_gemm_dequant
+    -> RMSNorm + RoPE + write into the exchange layout [P, s, h*d]         dax_rmsnorm_rope_pack
+       (V: the GEMM epilogue writes the exchange layout directly)
+    -> tokens->heads exchange, chunk by chunk while the next chunk is projected   (NCCL p2p group)
+    -> K smoothing + INT8/FP8 operand preparation, flash attention         dax_attn_prepare/forward
+    -> heads->tokens exchange per micro-batch while the next one is attended      (NCCL p2p group)
+    -> O projection reading the receive slabs in place                     dax_quant_rowwise + GEMM
+
+RoPE is applied before the exchange with this rank's slice of the rotary table; it is a per-token,
+per-head operation, so this equals the reference's rotation after the exchange
+(``attn_adapter.py:162-173``).  There is no CPU or eager fallback: non-CUDA input raises."""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from ... import ops
+from ...parallel import dist as para_dist
+from ...parallel.patches.wanx2_1_t2v_opt import micro_batch_bounds
+from ...parallel.ulysses import UlyssesExchange, chunk_bounds
+from ...quant.nn.dynamic import Linear as QLinear
+
+HEAD_DIM = 128
+
+
+class _Buffers:
+    """Per-(device, shape) scratch tensors shared by every layer (allocated by torch, once)."""
+
+    def __init__(self):
+        self.store: Dict[Tuple, torch.Tensor] = {}
+
+    def get(self, name: str, shape, dtype, device) -> torch.Tensor:
+        key = (name, tuple(shape), dtype, str(device))
+        t = self.store.get(key)
+        if t is None:
+            # drop same-name buffers of other shapes so that a resolution change does not leak
+            for k in [k for k in self.store if k[0] == name and k[3] == str(device)]:
+                del self.store[k]
+            t = torch.empty(shape, dtype=dtype, device=device)
+            self.store[key] = t
+        return t
+
+
+_BUFFERS = _Buffers()
+_ROPE_CACHE: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def _rope_tables(rotary_emb: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Complex ``[1, 1, S, 64]`` table -> fp32 cos / sin ``[S, 64]`` (cached per table)."""
+    key = (rotary_emb.data_ptr(), tuple(rotary_emb.shape), str(rotary_emb.device), rotary_emb.dtype)
+    hit = _ROPE_CACHE.get(key)
+    if hit is None:
+        if len(_ROPE_CACHE) > 8:
+            _ROPE_CACHE.clear()
+        r = torch.view_as_real(rotary_emb.reshape(-1, rotary_emb.shape[-1]))
+        hit = (r[..., 0].to(torch.float32).contiguous(), r[..., 1].to(torch.float32).contiguous())
+        _ROPE_CACHE[key] = hit
+    return hit
+
+
+class DAXWanAttnProcessor2_0:
+    def __init__(self, sp_size: int = 1, overlap_comm: bool = False, attention_mode: str = "sage",
+                 qkv_chunks: int = 4, o_micro_batches: int = 2):
+        """``sp_size`` / ``overlap_comm`` as in the reference.  ``attention_mode``: "sage" (INT8 Q.K^T,
+        FP8 P.V) or "f16" (fp16 contractions).  ``qkv_chunks``: token chunks of the Q/K/V projections
+        whose exchange overlaps the next chunk's GEMMs; ``o_micro_batches``: micro-batches of the O
+        path (2 in the reference)."""
+        if attention_mode not in ops.ATTN_MODES:
+            raise ValueError(f"attention_mode must be one of {sorted(ops.ATTN_MODES)}")
+        self.sp_size = sp_size
+        self.overlap_comm = overlap_comm
+        self.attention_mode = attention_mode
+        self.qkv_chunks = qkv_chunks
+        self.o_micro_batches = o_micro_batches
+        self._xchg: Optional[UlyssesExchange] = None
+
+    # ------------------------------------------------------------------------------------------
+    def _exchange(self) -> Optional[UlyssesExchange]:
+        if not para_dist.parallel_state.is_enable_sequence_parallel():
+            return None
+        if self._xchg is None:
+            ps = para_dist.parallel_state
+            self._xchg = UlyssesExchange(ps.get_sequence_parallel_group(), ps.get_sequence_parallel_size(),
+                                         ps.get_sequence_parallel_rank())
+        return self._xchg
+
+    @staticmethod
+    def _project(lin: nn.Module, x_rows: torch.Tensor, q_pair, *, out: torch.Tensor, ldo: int, col_group: int,
+                 group_stride: int, row_sumsq: Optional[torch.Tensor]) -> None:
+        """``out <- lin(x_rows)`` in the (grouped) layout given by ldo / col_group / group_stride."""
+        if isinstance(lin, QLinear):
+            lin._check_supported()
+            qx, sx = q_pair
+            lin.forward_quantized(qx, sx, out=out, ldo=ldo, out_col_group=col_group,
+                                  out_group_stride=group_stride, row_sumsq=row_sumsq)
+        else:  # float projection: library GEMM, then a strided copy into the layout
+            y = F.linear(x_rows, lin.weight, lin.bias)
+            rows, N = y.shape
+            dst = torch.as_strided(out, (N // col_group, rows, col_group), (group_stride, ldo, 1))
+            dst.copy_(y.view(rows, N // col_group, col_group).transpose(0, 1))
+
+    @staticmethod
+    def _quantize_for(lins, x_rows: torch.Tensor):
+        """One quantisation shared by all quantised projections of ``x_rows`` with the same input dtype."""
+        cache = {}
+        pairs = []
+        for lin in lins:
+            if isinstance(lin, QLinear):
+                if lin.input_dtype not in cache:
+                    cache[lin.input_dtype] = lin.quantize_input(x_rows)
+                pairs.append(cache[lin.input_dtype])
+            else:
+                pairs.append(None)
+        return pairs
+
+    # ------------------------------------------------------------------------------------------
+    def __call__(self, attn, hidden_states: torch.Tensor, encoder_hidden_states: Optional[torch.Tensor] = None,
+                 attention_mask: Optional[torch.Tensor] = None, rotary_emb: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if getattr(attn, "add_k_proj", None) is not None:
+            raise NotImplementedError("Wan I2V SP pararrel is not supported yet")
+        if attention_mask is not None:
+            raise NotImplementedError("The quantised attention kernel does not support `attention_mask`")
+        if not hidden_states.is_cuda:
+            raise RuntimeError("DAXWanAttnProcessor2_0 runs on CUDA tensors only; there is no CPU fallback")
+        if hidden_states.dtype not in (torch.bfloat16, torch.float16):
+            raise NotImplementedError(f"hidden_states must be bf16 or fp16, got {hidden_states.dtype}")
+        outs = []
+        for b in range(hidden_states.shape[0]):
+            ctx = None if encoder_hidden_states is None else encoder_hidden_states[b]
+            if ctx is None:
+                outs.append(self._self_attention(attn, hidden_states[b].contiguous(), rotary_emb))
+            else:
+                outs.append(self._cross_attention(attn, hidden_states[b].contiguous(), ctx.contiguous()))
+        out = outs[0].unsqueeze(0) if len(outs) == 1 else torch.stack(outs, 0)
+        return attn.to_out[1](out)  # dropout (identity at inference), as in the reference
+
+    # ------------------------------------------------------------------------------------------
+    def _self_attention(self, attn, x: torch.Tensor, rotary_emb: Optional[torch.Tensor]) -> torch.Tensor:
+        s, D = x.shape
+        H = attn.heads
+        dev, dt = x.device, x.dtype
+        xchg = self._exchange()
+        P = xchg.P if xchg is not None else 1
+        rank = xchg.rank if xchg is not None else 0
+        assert H % P == 0, f"Number of heads ({H}) must be divisible by the sequence parallel size ({P})!"
+        assert D == H * HEAD_DIM, f"hidden size {D} != heads {H} x {HEAD_DIM}"
+        h = H // P
+        hd = h * HEAD_DIM
+        S = s * P
+        overlap = self.overlap_comm and P > 1
+
+        cos = sin = None
+        if rotary_emb is not None:
+            cos, sin = _rope_tables(rotary_emb)
+            assert cos.shape[0] >= S, f"rotary table has {cos.shape[0]} rows, sequence has {S}"
+
+        # exchange layout [P, s, h*d]: slab p = heads of rank p; with P == 1 this is plain [s, D]
+        send = [_BUFFERS.get(f"send{i}", (P, s, hd), dt, dev) for i in range(3)]
+        recv = send if P == 1 else [_BUFFERS.get(f"recv{i}", (S, hd), dt, dev) for i in range(3)]
+        n_tiles = (D + 255) // 256
+
+        bounds = chunk_bounds(s, self.qkv_chunks if overlap else 1)
+        max_rows = max(bounds[i + 1] - bounds[i] for i in range(len(bounds) - 1))
+        works = []
+        lins = (attn.to_q, attn.to_k, attn.to_v)
+        norms = (attn.norm_q, attn.norm_k, None)
+        for c in range(len(bounds) - 1):
+            c0, c1 = bounds[c], bounds[c + 1]
+            rows = c1 - c0
+            x_rows = x[c0:c1]
+            pairs = self._quantize_for(lins, x_rows)
+            for i, (lin, norm) in enumerate(zip(lins, norms)):
+                dst = send[i].view(P * s, hd)[c0:]  # row c0 of slab 0; slabs are s*hd apart
+                if i == 2 or (norm is None and cos is None):
+                    # no per-row post-processing: the GEMM writes the exchange layout itself
+                    self._project(lin, x_rows, pairs[i], out=dst, ldo=hd, col_group=hd, group_stride=s * hd,
+                                  row_sumsq=None)
+                    continue
+                tmp = _BUFFERS.get("proj_tmp", (max_rows, D), dt, dev)[:rows]
+                fused = isinstance(lin, QLinear) and norm is not None
+                ss = _BUFFERS.get("row_sumsq", (max_rows, n_tiles), torch.float32, dev)[:rows] if fused else None
+                self._project(lin, x_rows, pairs[i], out=tmp, ldo=D, col_group=D, group_stride=0, row_sumsq=ss)
+                w = getattr(norm, "weight", None) if norm is not None else None
+                ops.rmsnorm_rope_pack(tmp, norm_weight=w, do_norm=norm is not None,
+                                      eps=getattr(norm, "eps", 1e-6) if norm is not None else 1e-6,
+                                      rope_cos=cos, rope_sin=sin, token_offset=rank * s + c0, row_sumsq=ss,
+                                      out=dst, ldo=hd, col_group=hd, group_stride=s * hd)
+            if P > 1:
+                works.append(xchg.tokens_to_heads(send, recv, c0, c1, async_op=overlap))
+        for w in works:
+            w.wait()
+
+        # attention over the full sequence of the local heads: [S, h, d] viewed as [1, h, S, d]
+        def bhsd(t):
+            return t.view(1, S, h, HEAD_DIM).transpose(1, 2)
+
+        plan = ops.attn_prepare(bhsd(recv[0]), bhsd(recv[1]), bhsd(recv[2]), self.attention_mode,
+                                1.0 / math.sqrt(HEAD_DIM))
+        attn_out = _BUFFERS.get("attn_out", (S, hd), dt, dev)
+        o_lin = attn.to_out[0]
+        out = torch.empty((s, D), dtype=dt, device=dev)
+
+        if P == 1:
+            ops.attn_forward(plan, bhsd(attn_out))
+            pair = self._quantize_for((o_lin,), attn_out)[0]
+            self._project(o_lin, attn_out, pair, out=out, ldo=D, col_group=D, group_stride=0, row_sumsq=None)
+            return out
+
+        # O path: attend micro-batch i, start its exchange, and project micro-batch i-1 meanwhile
+        m = self.o_micro_batches if overlap else 1
+        mb = micro_batch_bounds(s, m)
+        pending = []
+        for i in range(m):
+            b0, b1 = mb[i], mb[i + 1]
+            if b1 == b0:
+                continue
+            ops.attn_forward(plan, bhsd(attn_out), q_begin=b0, q_end=b1, n_ranges=P, range_stride=s)
+            o_recv = _BUFFERS.get(f"o_recv{i}", (P, b1 - b0, hd), dt, dev)
+            work = xchg.heads_to_tokens(attn_out, o_recv, s, b0, b1, async_op=overlap)
+            pending.append((work, o_recv, b0, b1))
+            if len(pending) > 1:
+                self._o_project(o_lin, pending.pop(0), out, P, hd, D)
+        while pending:
+            self._o_project(o_lin, pending.pop(0), out, P, hd, D)
+        return out
+
+    def _o_project(self, o_lin, item, out: torch.Tensor, P: int, hd: int, D: int) -> None:
+        work, o_recv, b0, b1 = item
+        work.wait()
+        n = b1 - b0
+        if isinstance(o_lin, QLinear):
+            o_lin._check_supported()
+            # the quantiser reads the receive slabs [P, n, h*d] in place as a [n, D] matrix
+            qx, sx = ops.quant_rowwise(o_recv, o_lin.input_dtype, col_group=hd, group_stride=n * hd, rows=n, cols=D,
+                                       ldx=hd)
+            o_lin.forward_quantized(qx, sx, out=out[b0:b1], ldo=D)
+        else:
+            xm = o_recv.permute(1, 0, 2).reshape(n, D)
+            out[b0:b1] = F.linear(xm, o_lin.weight, o_lin.bias)
+
+    # ------------------------------------------------------------------------------------------
+    def _cross_attention(self, attn, x: torch.Tensor, ctx: torch.Tensor) -> torch.Tensor:
+        """Cross-attention (``attn2``): queries are this rank's tokens, keys/values the replicated text
+        context.  Every query row attends to the whole context locally, so nothing is exchanged; the
+        reference exchanges Q/K/V/O here too and attends over P identical copies of the context,
+        which gives the same softmax (``attn_adapter.py:96-101,125-141``)."""
+        s, D = x.shape
+        H = attn.heads
+        dev, dt = x.device, x.dtype
+        Sk = ctx.shape[0]
+        q = _BUFFERS.get("xq", (s, D), dt, dev)
+        k = _BUFFERS.get("xk", (Sk, D), dt, dev)
+        v = _BUFFERS.get("xv", (Sk, D), dt, dev)
+        n_tiles = (D + 255) // 256
+        for lin, norm, src, dst in ((attn.to_q, attn.norm_q, x, q), (attn.to_k, attn.norm_k, ctx, k),
+                                    (attn.to_v, None, ctx, v)):
+            pair = self._quantize_for((lin,), src)[0]
+            if norm is None:
+                self._project(lin, src, pair, out=dst, ldo=D, col_group=D, group_stride=0, row_sumsq=None)
+                continue
+            rows = src.shape[0]
+            tmp = _BUFFERS.get("xproj_tmp", (rows, D), dt, dev)
+            fused = isinstance(lin, QLinear)
+            ss = _BUFFERS.get("xrow_sumsq", (rows, n_tiles), torch.float32, dev) if fused else None
+            self._project(lin, src, pair, out=tmp, ldo=D, col_group=D, group_stride=0, row_sumsq=ss)
+            ops.rmsnorm_rope_pack(tmp, norm_weight=getattr(norm, "weight", None), do_norm=True,
+                                  eps=getattr(norm, "eps", 1e-6), row_sumsq=ss, out=dst, ldo=D)
+
+        def bhsd(t, n):
+            return t.view(1, n, H, HEAD_DIM).transpose(1, 2)
+
+        o = _BUFFERS.get("xo", (s, D), dt, dev)
+        plan = ops.attn_prepare(bhsd(q, s), bhsd(k, Sk), bhsd(v, Sk), self.attention_mode, 1.0 / math.sqrt(HEAD_DIM))
+        ops.attn_forward(plan, bhsd(o, s))
+        o_lin = attn.to_out[0]
+        out = torch.empty((s, D), dtype=dt, device=dev)
+        pair = self._quantize_for((o_lin,), o)[0]
+        self._project(o_lin, o, pair, out=out, ldo=D, col_group=D, group_stride=0, row_sumsq=None)
+        return out
+
+
+def _attention_classes():
+    classes = []
+    try:  # the real thing, when diffusers is installed
+        from diffusers.models.attention_processor import Attention as DiffusersAttention
+        classes.append(DiffusersAttention)
+    except Exception:
+        pass
+    from .modules import Attention
+    classes.append(Attention)
+    return tuple(classes)
+
+
+def replace_wan_attention(pipe, sp_size: int = 1, overlap_comm: bool = False, **processor_kwargs) -> None:
+    """Install the processor on every attention module of ``pipe.transformer``
+    (``dax/adapters/wan/attn_adapter.py:307-312``)."""
+    classes = _attention_classes()
+    for _, m in pipe.transformer.named_modules():
+        if isinstance(m, classes):
+            m.set_processor(DAXWanAttnProcessor2_0(sp_size=sp_size, overlap_comm=overlap_comm, **processor_kwargs))

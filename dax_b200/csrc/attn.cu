@@ -70,7 +70,8 @@ struct AttnParams {
   int64_t o_sb, o_sh, o_st;  // element strides of o: batch, head, token
   int heads;
   int Sq, Sk, Sq_pad, Sk_pad;
-  int q_begin, q_end;
+  int q_begin, q_end;      // first query range
+  int n_ranges, range_stride, tiles_per_range;
   int out_bf16;
 };
 
@@ -201,7 +202,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int bh = blockIdx.y;
-  const int q0 = p.q_begin + blockIdx.x * 256;
+  const int range = blockIdx.x / p.tiles_per_range;
+  const int q0 = p.q_begin + range * p.range_stride + (blockIdx.x % p.tiles_per_range) * 256;
+  const int q_stop = min(p.q_end + range * p.range_stride, p.Sq);
   const int n_kv = p.Sk_pad / 128;
 
   if (threadIdx.x == 0) {
@@ -311,7 +314,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const uint32_t o_tmem = tmem_base + lane_base + 256 + x * 128;
     uint8_t* p_tile = smem + L::OFF_P + x * L::P_TILE;
     const int q_row = q0 + x * 128 + r;
-    const float sq = p.q_scale[static_cast<int64_t>(bh) * p.Sq_pad + q_row];
+    const float sq = q_row < p.Sq ? p.q_scale[static_cast<int64_t>(bh) * p.Sq_pad + q_row] : 1.f;
     const float* ks = p.k_scale + static_cast<int64_t>(bh) * n_kv;
     float m = -INFINITY, l = 0.f;
     float ks_next = ks[0];
@@ -360,7 +363,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     if (ok && mbar_wait(&s_full[x], n_kv & 1u, abort_flag)) {
       tc_fence_after_sync();
       const float inv_l = 1.f / l;
-      const bool store = q_row < p.q_end && q_row < p.Sq;
+      const bool store = q_row < q_stop;
       const int b = bh / p.heads, h = bh % p.heads;
       uint16_t* orow = static_cast<uint16_t*>(p.o) + b * p.o_sb + h * p.o_sh + static_cast<int64_t>(q_row) * p.o_st;
 #pragma unroll
@@ -428,7 +431,7 @@ int launch_fwd(const AttnWorkspace& ws, const AttnParams& p, int64_t BH, cudaStr
     if (rc != DAX_OK) return rc;
   }
   DAX_CUDA(cudaFuncSetAttribute(attn_fwd_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-  dim3 grid(static_cast<unsigned>((p.q_end - p.q_begin + 255) / 256), static_cast<unsigned>(BH));
+  dim3 grid(static_cast<unsigned>(p.n_ranges * p.tiles_per_range), static_cast<unsigned>(BH));
   attn_fwd_kernel<MODE><<<grid, ATT_THREADS, L::TOTAL, st>>>(map_q, map_k, map_v, p);
   DAX_CUDA(cudaGetLastError());
   return DAX_OK;
@@ -438,8 +441,9 @@ int launch_fwd(const AttnWorkspace& ws, const AttnParams& p, int64_t BH, cudaStr
 }  // namespace dax
 
 extern "C" int dax_attn_forward(void* o, int dtype, int64_t B, int64_t heads, int64_t Sq, int64_t Sk,
-                                int64_t o_strides[3], int64_t q_begin, int64_t q_end, int mode, void* workspace,
-                                size_t workspace_bytes, void* stream) {
+                                int64_t o_strides[3], int64_t q_begin, int64_t q_end, int64_t n_ranges,
+                                int64_t range_stride, int mode, void* workspace, size_t workspace_bytes,
+                                void* stream) {
   using namespace dax;
   DAX_REQUIRE(o && workspace && o_strides, DAX_ERR_INVALID, "attn_forward: null pointer");
   DAX_REQUIRE(dtype == DAX_BF16 || dtype == DAX_F16, DAX_ERR_UNSUPPORTED, "attn_forward: dtype %d is not BF16/F16", dtype);
@@ -448,7 +452,10 @@ extern "C" int dax_attn_forward(void* o, int dtype, int64_t B, int64_t heads, in
   if (rc != DAX_OK) return rc;
   DAX_REQUIRE(q_begin >= 0 && q_begin <= q_end && q_end <= Sq, DAX_ERR_INVALID,
               "attn_forward: bad query range [%lld, %lld) for Sq=%lld", (long long)q_begin, (long long)q_end, (long long)Sq);
-  DAX_REQUIRE(q_begin % 256 == 0, DAX_ERR_ALIGN, "attn_forward: q_begin=%lld must be a multiple of 256", (long long)q_begin);
+  DAX_REQUIRE(n_ranges >= 1 && (n_ranges == 1 || range_stride >= q_end - q_begin) &&
+                  q_end + (n_ranges - 1) * range_stride <= Sq,
+              DAX_ERR_INVALID, "attn_forward: %lld ranges of stride %lld do not fit Sq=%lld", (long long)n_ranges,
+              (long long)range_stride, (long long)Sq);
   if (q_begin == q_end) return DAX_OK;
   DAX_REQUIRE(aligned16(o) && o_strides[0] % 8 == 0 && o_strides[1] % 8 == 0 && o_strides[2] % 8 == 0, DAX_ERR_ALIGN,
               "attn_forward: o must be 16-byte aligned with strides that are multiples of 8 elements");
@@ -462,6 +469,8 @@ extern "C" int dax_attn_forward(void* o, int dtype, int64_t B, int64_t heads, in
   p.Sq = static_cast<int>(Sq); p.Sk = static_cast<int>(Sk);
   p.Sq_pad = static_cast<int>(ws.Sq_pad); p.Sk_pad = static_cast<int>(ws.Sk_pad);
   p.q_begin = static_cast<int>(q_begin); p.q_end = static_cast<int>(q_end);
+  p.n_ranges = static_cast<int>(n_ranges); p.range_stride = static_cast<int>(range_stride);
+  p.tiles_per_range = static_cast<int>((q_end - q_begin + 255) / 256);
   p.out_bf16 = dtype == DAX_BF16;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (mode == DAX_ATTN_QK_I8_PV_F8) return launch_fwd<DAX_ATTN_QK_I8_PV_F8>(ws, p, B * heads, st);

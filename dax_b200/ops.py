@@ -154,14 +154,17 @@ def attn_prepare(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mode: str = 
     return AttentionPlan(B, heads, Sq, Sk, m, ws, q.dtype)
 
 
-def attn_forward(plan: AttentionPlan, out: torch.Tensor, q_begin: int = 0, q_end: Optional[int] = None) -> torch.Tensor:
-    """Run the flash pass for queries ``[q_begin, q_end)`` into ``out`` (a ``[B, heads, Sq, 128]`` view)."""
+def attn_forward(plan: AttentionPlan, out: torch.Tensor, q_begin: int = 0, q_end: Optional[int] = None,
+                 n_ranges: int = 1, range_stride: int = 0) -> torch.Tensor:
+    """Run the flash pass for the query rows ``[q_begin + r*range_stride, q_end + r*range_stride)``,
+    ``r < n_ranges``, into ``out`` (a ``[B, heads, Sq, 128]`` view)."""
     _need_cuda(out)
     if q_end is None:
         q_end = plan.Sq
     assert out.shape == (plan.B, plan.heads, plan.Sq, 128) and out.dtype == plan.dtype
     check(load().dax_attn_forward(out.data_ptr(), _dt(out.dtype), plan.B, plan.heads, plan.Sq, plan.Sk,
-                                  _bhsd_strides(out), q_begin, q_end, plan.mode, plan.workspace.data_ptr(),
+                                  _bhsd_strides(out), q_begin, q_end, n_ranges, range_stride, plan.mode,
+                                  plan.workspace.data_ptr(),
                                   plan.workspace.numel(), _stream()))
     return out
 

@@ -134,9 +134,11 @@ int dax_rmsnorm_rope_pack(const void* x, int dtype, int64_t s, int64_t D, int64_
  *   dax_attn_prepare   K: per-(batch, head, channel) mean over the sequence removed, then INT8 per
  *                      block of 128 tokens (or fp16); Q: softmax scale folded in, INT8 per token (or
  *                      fp16); V: FP8 e4m3 with a per-channel scale, stored transposed (or fp16).
- *   dax_attn_forward   flash-style pass over the prepared operands; may be called for any token
- *                      range [q_begin, q_end) of the queries (the O-path micro-batches call it once
- *                      per range), q_begin a multiple of 256.
+ *   dax_attn_forward   flash-style pass over the prepared operands for the query rows
+ *                      [q_begin + r*range_stride, q_end + r*range_stride), r = 0 .. n_ranges-1
+ *                      (one call per O-path micro-batch: the i-th slice of every destination rank's
+ *                      token block, dax/parallel/patches/wanx2_1_t2v_opt/micro_batch_layer.py:14-29);
+ *                      n_ranges = 1, q_begin = 0, q_end = Sq for all queries.
  * sm_scale: softmax scale (1/sqrt(128) in the reference).
  * ------------------------------------------------------------------------------------------- */
 size_t dax_attn_workspace_bytes(int64_t B, int64_t heads, int64_t Sq, int64_t Sk, int mode);
@@ -146,8 +148,8 @@ int dax_attn_prepare(const void* q, const void* k, const void* v, int dtype, int
                      float sm_scale, int mode, void* workspace, size_t workspace_bytes, void* stream);
 
 int dax_attn_forward(void* o, int dtype, int64_t B, int64_t heads, int64_t Sq, int64_t Sk, int64_t o_strides[3],
-                     int64_t q_begin, int64_t q_end, int mode, void* workspace, size_t workspace_bytes,
-                     void* stream);
+                     int64_t q_begin, int64_t q_end, int64_t n_ranges, int64_t range_stride, int mode,
+                     void* workspace, size_t workspace_bytes, void* stream);
 
 #ifdef __cplusplus
 }

@@ -99,7 +99,8 @@ def main():
 
     net = Net()
     quantize_dynamic(net, {"": int8_cfg(), "condition_embedder": None, "proj_out": None})
-    torch.save({n: type(m).__name__ for n, m in net.named_modules()}, os.path.join(HERE, "swap.pt"))
+    torch.save({n: (type(m).__name__, hasattr(m, "qweight")) for n, m in net.named_modules()},
+               os.path.join(HERE, "swap.pt"))
 
     # ---- micro-batch strategy + exchange layouts (P ranks emulated in-process) ----
     from dax.parallel.patches.wanx2_1_t2v_opt.layer import _generate_layout_params, post_all2all, pre_all2all_fun
