@@ -20,6 +20,47 @@ ATTN_MODES = {"sage": _lib.DAX_ATTN_QK_I8_PV_F8, "int8_fp8": _lib.DAX_ATTN_QK_I8
               "f16": _lib.DAX_ATTN_QK_F16_PV_F16}
 
 
+class _Trace:
+    """Optional launch accounting: number of library kernels launched and, when timing is on, CUDA
+    events around each wrapper on the stream it launches on (used by the benchmark's roofline leg)."""
+
+    KERNELS_PER_CALL = {"linear_dynamic": 2, "quant_rowwise": 1, "gemm_dequant": 1, "rmsnorm_rope_pack": 1, "attn_prepare": 5, "attn_forward": 1}
+
+    def __init__(self):
+        self.launches = 0
+        self.timing = False
+        self.events = []
+
+    def reset(self, timing: bool = False):
+        self.launches, self.timing, self.events = 0, timing, []
+
+    def begin(self, name):
+        self.launches += self.KERNELS_PER_CALL[name]
+        if not self.timing:
+            return None
+        e0 = torch.cuda.Event(enable_timing=True)
+        e0.record(torch.cuda.current_stream())
+        return (name, e0)
+
+    def end(self, tok, meta=None):
+        if tok is None:
+            return
+        e1 = torch.cuda.Event(enable_timing=True)
+        e1.record(torch.cuda.current_stream())
+        self.events.append((tok[0], tok[1], e1, meta))
+
+    def summary(self):
+        """name -> (calls, total milliseconds, list of meta) after a device synchronise."""
+        out = {}
+        for name, e0, e1, meta in self.events:
+            c, t, m = out.get(name, (0, 0.0, []))
+            out[name] = (c + 1, t + e0.elapsed_time(e1), m + [meta])
+        return out
+
+
+TRACE = _Trace()
+
+
 def _dt(dtype: torch.dtype) -> int:
     if dtype not in _DT:
         raise NotImplementedError(f"dax_b200: dtype {dtype} is not supported")
@@ -59,8 +100,10 @@ def quant_rowwise(x: torch.Tensor, q_dtype: torch.dtype, *, col_group: Optional[
         M, K, ld, cg, gs, src = rows, cols, ldx, col_group, group_stride, x
     q = torch.empty((M, K), dtype=q_dtype, device=x.device)
     scale = torch.empty((M, 1), dtype=torch.float32, device=x.device)
+    tok = TRACE.begin("quant_rowwise")
     check(load().dax_quant_rowwise(src.data_ptr(), _dt(x.dtype), M, K, ld, cg, gs, q.data_ptr(), _dt(q_dtype),
                                    scale.data_ptr(), _stream()))
+    TRACE.end(tok, (M, K, x.element_size()))
     return q, scale
 
 
@@ -79,10 +122,33 @@ def gemm_dequant(qx: torch.Tensor, sx: torch.Tensor, qw: torch.Tensor, sw: torch
         ldo = N
     if out_col_group is None:
         out_col_group = N
+    tok = TRACE.begin("gemm_dequant")
     check(load().dax_gemm_dequant(qx.data_ptr(), _dt(qx.dtype), sx.data_ptr(), qw.data_ptr(), _dt(qw.dtype),
                                   sw.data_ptr(), _ptr(bias), _dt(bias.dtype) if bias is not None else 0,
                                   out.data_ptr(), _dt(out_dtype), M, N, K, ldo, out_col_group, out_group_stride,
                                   _ptr(row_sumsq), _ptr(acc_dump), _stream()))
+    TRACE.end(tok, (M, N, K))
+    return out
+
+
+def linear_dynamic(x: torch.Tensor, qw: torch.Tensor, sw: torch.Tensor, bias: Optional[torch.Tensor],
+                   act_dtype: torch.dtype, out_dtype: torch.dtype) -> torch.Tensor:
+    """``dynamic.Linear.forward`` in one library call: quantise ``x [M, K]`` per token, multiply by the
+    quantised weight ``qw [N, K]``, de-quantise, add the bias.  The workspace comes from torch."""
+    _need_cuda(x, qw, sw, bias)
+    M, K = x.shape
+    N = qw.shape[0]
+    assert x.stride(1) == 1 and qw.is_contiguous()
+    n = load().dax_linear_dynamic_workspace_bytes(M, K)
+    ws = torch.empty(n + 256, dtype=torch.uint8, device=x.device)
+    off = (-ws.data_ptr()) % 256
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    tok = TRACE.begin("linear_dynamic")
+    check(load().dax_linear_dynamic(x.data_ptr(), _dt(x.dtype), M, K, x.stride(0) if M > 1 else K, qw.data_ptr(),
+                                    _dt(qw.dtype), _dt(act_dtype), sw.data_ptr(), _ptr(bias),
+                                    _dt(bias.dtype) if bias is not None else 0, out.data_ptr(), _dt(out_dtype), N, N,
+                                    ws.data_ptr() + off, n, _stream()))
+    TRACE.end(tok, (M, N, K))
     return out
 
 
@@ -101,10 +167,12 @@ def rmsnorm_rope_pack(x: torch.Tensor, *, norm_weight: Optional[torch.Tensor], d
     if col_group is None:
         col_group = D
     n_part = row_sumsq.shape[1] if row_sumsq is not None else 0
+    tok = TRACE.begin("rmsnorm_rope_pack")
     check(load().dax_rmsnorm_rope_pack(x.data_ptr(), _dt(x.dtype), s, D, x.stride(0), _ptr(row_sumsq), n_part,
                                        1 if do_norm else 0, _ptr(norm_weight), float(eps), _ptr(rope_cos),
                                        _ptr(rope_sin), token_offset, out.data_ptr(), ldo, col_group, group_stride,
                                        _stream()))
+    TRACE.end(tok, (s, D))
     return out
 
 
@@ -148,9 +216,11 @@ def attn_prepare(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mode: str = 
     ws = attn_workspace(B, heads, Sq, Sk, m, q.device)
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(d)
+    tok = TRACE.begin("attn_prepare")
     check(load().dax_attn_prepare(q.data_ptr(), k.data_ptr(), v.data_ptr(), _dt(q.dtype), B, heads, Sq, Sk,
                                   _bhsd_strides(q), _bhsd_strides(k), _bhsd_strides(v), float(sm_scale), m,
                                   ws.data_ptr(), ws.numel(), _stream()))
+    TRACE.end(tok, (B, heads, Sq, Sk))
     return AttentionPlan(B, heads, Sq, Sk, m, ws, q.dtype)
 
 
@@ -162,10 +232,12 @@ def attn_forward(plan: AttentionPlan, out: torch.Tensor, q_begin: int = 0, q_end
     if q_end is None:
         q_end = plan.Sq
     assert out.shape == (plan.B, plan.heads, plan.Sq, 128) and out.dtype == plan.dtype
+    tok = TRACE.begin("attn_forward")
     check(load().dax_attn_forward(out.data_ptr(), _dt(out.dtype), plan.B, plan.heads, plan.Sq, plan.Sk,
                                   _bhsd_strides(out), q_begin, q_end, n_ranges, range_stride, plan.mode,
                                   plan.workspace.data_ptr(),
                                   plan.workspace.numel(), _stream()))
+    TRACE.end(tok, (plan.B, plan.heads, (q_end - q_begin) * n_ranges, plan.Sk))
     return out
 
 

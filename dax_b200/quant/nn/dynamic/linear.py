@@ -81,9 +81,13 @@ class Linear(nn.Module):
         self._check_supported()
         if not input.is_cuda:
             raise RuntimeError("dax_b200.quant.nn.dynamic.Linear runs on CUDA only; there is no CPU fallback")
+        from ....ops import linear_dynamic
         prev_dims = input.shape[:-1]
-        qinput, input_scale = self.quantize_input(input)
-        out = self.forward_quantized(qinput, input_scale)
+        x2 = input.reshape(-1, self.in_features)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        out = linear_dynamic(x2, self.qweight, self.weight_scale.reshape(-1), self.bias, self.input_dtype,
+                             self.out_dtype)
         return out.view(*prev_dims, self.out_features)
 
     def extra_repr(self) -> str:

@@ -105,6 +105,19 @@ int dax_gemm_f8_dequant(const void* qx, int a_dtype, const float* sx, const void
                         int64_t K, int64_t ldo, float* row_sumsq, float* acc_dump, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * One-call dynamic quantised linear = dax_quant_rowwise followed by dax_gemm_dequant, i.e. the whole of
+ * dax.quant.nn.dynamic.Linear.forward (dax/quant/nn/dynamic/linear.py:143-228) for a plain row-major
+ * x [M, K] (ldx) and out [M, N] (ldo).  The quantised activations and their scales sit in `workspace`
+ * (256-byte aligned, at least dax_linear_dynamic_workspace_bytes(M, K)) between the two launches.
+ * act_dtype: I8 with I8 weights, E4M3 / E5M2 with FP8 weights (w_dtype).
+ * ------------------------------------------------------------------------------------------- */
+size_t dax_linear_dynamic_workspace_bytes(int64_t M, int64_t K);
+
+int dax_linear_dynamic(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, const void* qw, int w_dtype,
+                       int act_dtype, const float* sw, const void* bias, int bias_dtype, void* out, int out_dtype,
+                       int64_t N, int64_t ldo, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * RMSNorm over the full hidden dimension + 3-D rotary embedding + pack into the exchange layout.
  * Replaces the norm_q / norm_k call sites (dax/adapters/wan/attn_adapter.py:82-85,108-109,121-122),
  * apply_rotary_emb (attn_adapter.py:164-173; the reference rotates after the exchange, which is

@@ -306,3 +306,21 @@ def test_attention_rows_are_convex_combinations(ops):
     o = ops.attention(q, k, v2, mode="f16").float().cpu()
     ref = torch.nn.functional.scaled_dot_product_attention(q[:, :, 5000:5256].float().cpu(), k.float().cpu(), v2.float().cpu())
     assert O.rel_l2(o[:, :, 5000:5256], ref) <= 1e-2
+
+
+# ---- one-call dynamic linear ---------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K", [(40, 192, 256), (512, 5120, 4096), (1000, 1536, 1536)])
+def test_linear_dynamic_matches_two_step(ops, M, N, K):
+    torch.manual_seed(M)
+    x = torch.randn(M, K).bfloat16()
+    w = (torch.randn(N, K) * 0.02).bfloat16()
+    b = (torch.randn(N) * 0.1).bfloat16()
+    for wdt, adt in ((torch.int8, torch.int8), (torch.float8_e4m3fn, torch.float8_e4m3fn)):
+        qw, sw = O.quantize_weight(w, wdt)
+        swd = sw.to(DEV).reshape(-1).contiguous()
+        y = ops.linear_dynamic(x.to(DEV), qw.to(DEV), swd, b.to(DEV), adt, torch.bfloat16)
+        qx, sx = ops.quant_rowwise(x.to(DEV), adt)
+        y2 = ops.gemm_dequant(qx, sx, qw.to(DEV), swd, b.to(DEV), torch.bfloat16)
+        assert torch.equal(y, y2)
+        if wdt == torch.int8:
+            assert torch.equal(y.cpu(), O.linear_int8(x, qw, sw, b, torch.bfloat16))
