@@ -34,6 +34,8 @@ SIGNATURES = {
     "dax_linear_dynamic_workspace_bytes": (c_size_t, [c_int64, c_int64]),
     "dax_linear_dynamic": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                    c_int, c_void_p, c_int, c_int64, c_int64, c_void_p, c_size_t, c_void_p]),
+    "dax_linear_dynamic_static": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int, c_int, c_void_p,
+                                          c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_void_p]),
     "dax_rmsnorm_rope_pack": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int,
                                       c_void_p, c_float, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64,
                                       c_int64, c_void_p]),

@@ -118,6 +118,32 @@ int dax_linear_dynamic(const void* x, int x_dtype, int64_t M, int64_t K, int64_t
                        int64_t N, int64_t ldo, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * dax_linear_dynamic for callers that cannot allocate device memory.  It has no counterpart in the
+ * reference.  Some hosts of this library hand it nothing but their input and output buffers and are
+ * not allowed to call cudaMalloc on the path that runs the layer: a serving runtime whose memory pool
+ * is carved up at start-up, a binding from another language that owns no CUDA allocator, code that
+ * runs where an allocation would stall every stream of the device.  For them the quantised
+ * activations and scales go to a fixed buffer that is part of the library image instead of a
+ * workspace argument.
+ *   - Limit: dax_linear_dynamic_workspace_bytes(M, K) <= DAX_LINEAR_STATIC_SCRATCH_BYTES (8 MiB; e.g.
+ *     the 512 x 4096 text-context projections, or 1024 rows of a 5120-wide layer).  Larger problems
+ *     are rejected with DAX_ERR_UNSUPPORTED and a message; nothing is launched.
+ *   - Cost: every GPU that loads the library keeps those 8 MiB until the process exits.
+ *   - The first call on each device looks up the buffer's device address (no allocation); make that
+ *     first call before starting any stream capture.
+ *   - All calls on a device share the one buffer.  Calls that may run at the same time on the GPU
+ *     (different streams) race on it: keep them on one stream or order them with events.  The buffer
+ *     keeps the previous call's bytes; the entry point never relies on its contents.
+ *   - The call itself performs no cudaMalloc / cudaFree and uses no allocating library routine.
+ * Arguments as dax_linear_dynamic, without the workspace.
+ * ------------------------------------------------------------------------------------------- */
+#define DAX_LINEAR_STATIC_SCRATCH_BYTES (8u << 20)
+
+int dax_linear_dynamic_static(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, const void* qw,
+                              int w_dtype, int act_dtype, const float* sw, const void* bias, int bias_dtype,
+                              void* out, int out_dtype, int64_t N, int64_t ldo, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * RMSNorm over the full hidden dimension + 3-D rotary embedding + pack into the exchange layout.
  * Replaces the norm_q / norm_k call sites (dax/adapters/wan/attn_adapter.py:82-85,108-109,121-122),
  * apply_rotary_emb (attn_adapter.py:164-173; the reference rotates after the exchange, which is
