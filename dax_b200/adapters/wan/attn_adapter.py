@@ -171,7 +171,7 @@ class DAXWanAttnProcessor2_0:
         # exchange layout [P, s, h*d]: slab p = heads of rank p; with P == 1 this is plain [s, D]
         send = [_BUFFERS.get(f"send{i}", (P, s, hd), dt, dev) for i in range(3)]
         recv = send if P == 1 else [_BUFFERS.get(f"recv{i}", (S, hd), dt, dev) for i in range(3)]
-        n_tiles = (D + 255) // 256
+        n_tiles = 2 * ((D + 255) // 256)  # sum-of-squares partials: one per 128 columns
 
         bounds = chunk_bounds(s, self.qkv_chunks if overlap else 1)
         max_rows = max(bounds[i + 1] - bounds[i] for i in range(len(bounds) - 1))
@@ -265,7 +265,7 @@ class DAXWanAttnProcessor2_0:
         q = _BUFFERS.get("xq", (s, D), dt, dev)
         k = _BUFFERS.get("xk", (Sk, D), dt, dev)
         v = _BUFFERS.get("xv", (Sk, D), dt, dev)
-        n_tiles = (D + 255) // 256
+        n_tiles = 2 * ((D + 255) // 256)  # sum-of-squares partials: one per 128 columns
         for lin, norm, src, dst in ((attn.to_q, attn.norm_q, x, q), (attn.to_k, attn.norm_k, ctx, k),
                                     (attn.to_v, None, ctx, v)):
             pair = self._quantize_for((lin,), src)[0]

@@ -93,12 +93,6 @@ __device__ __forceinline__ void mma_tile(uint32_t d_tmem, uint32_t a_addr, uint3
   }
 }
 
-__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
-  uint16_t lo, hi;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
-  return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
-}
 __device__ __forceinline__ uint32_t pack_f16x2(float a, float b) {
   uint32_t r;
   asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
@@ -116,22 +110,30 @@ template <int MODE, bool FULL>
 __device__ __forceinline__ float row_max(const uint32_t (&sv)[128], float cmul, int valid) {
   using C = AttnCfg<MODE>;
   if constexpr (C::QK_KIND == KIND_I8) {
-    int imax = INT_MIN;
+    int imax[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN};
 #pragma unroll
     for (int i = 0; i < 128; ++i)
-      if (FULL || i < valid) imax = max(imax, static_cast<int>(sv[i]));
-    return static_cast<float>(imax) * cmul;
+      if (FULL || i < valid) imax[i & 3] = max(imax[i & 3], static_cast<int>(sv[i]));
+    return static_cast<float>(max(max(imax[0], imax[1]), max(imax[2], imax[3]))) * cmul;
   } else {
-    float fmx = -INFINITY;
+    float fmx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
     for (int i = 0; i < 128; ++i)
-      if (FULL || i < valid) fmx = fmaxf(fmx, __uint_as_float(sv[i]));
-    return fmx * cmul;
+      if (FULL || i < valid) fmx[i & 3] = fmaxf(fmx[i & 3], __uint_as_float(sv[i]));
+    return fmaxf(fmaxf(fmx[0], fmx[1]), fmaxf(fmx[2], fmx[3])) * cmul;
   }
 }
 
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+  uint16_t lo, hi;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
+  return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+
 // p_i = 2^(s_i * cmul + off) for the row held in sv; converts to the P format, writes the row into
-// the K-major 128-byte-swizzled P tile and returns the fp32 row sum.
+// the K-major 128-byte-swizzled P tile and returns the fp32 row sum (four independent partial sums
+// keep the add chain short).
 template <int MODE, bool FULL>
 __device__ __forceinline__ float exp_and_store(const uint32_t (&sv)[128], float cmul, float off, int valid,
                                                uint8_t* p_tile, int r) {
@@ -144,7 +146,7 @@ __device__ __forceinline__ float exp_and_store(const uint32_t (&sv)[128], float 
     else v = ex2(fmaf(__uint_as_float(sv[i]), cmul, off));
     return (FULL || i < valid) ? v : 0.f;
   };
-  float sum = 0.f;
+  float sum[4] = {0.f, 0.f, 0.f, 0.f};
   if constexpr (C::EP == 1) {
 #pragma unroll
     for (int ck = 0; ck < 8; ++ck) {
@@ -152,7 +154,7 @@ __device__ __forceinline__ float exp_and_store(const uint32_t (&sv)[128], float 
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         e[i] = pv(16 * ck + i);
-        sum += e[i];
+        sum[i & 3] += e[i];
       }
       uint4 w;
       w.x = pack_e4m3x4(e[0], e[1], e[2], e[3]);
@@ -168,7 +170,7 @@ __device__ __forceinline__ float exp_and_store(const uint32_t (&sv)[128], float 
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         e[i] = pv(8 * ck + i);
-        sum += e[i];
+        sum[i & 3] += e[i];
       }
       uint4 w;
       w.x = pack_f16x2(e[0], e[1]);
@@ -178,7 +180,7 @@ __device__ __forceinline__ float exp_and_store(const uint32_t (&sv)[128], float 
       *reinterpret_cast<uint4*>(p_tile + (ck >> 3) * BOX_BYTES + r * 128 + (((ck & 7) ^ (r & 7)) << 4)) = w;
     }
   }
-  return sum;
+  return (sum[0] + sum[1]) + (sum[2] + sum[3]);
 }
 
 template <int MODE>

@@ -8,8 +8,9 @@
 //   warp 1      MMA issuer: tcgen05.mma kind::i8 / kind::f8f6f4, 128x256 accumulator in tensor memory,
 //               two accumulator buffers (2 x 256 columns) so the epilogue of tile i overlaps the
 //               main loop of tile i+1
-//   warps 2..5  epilogue: tcgen05.ld 32 columns at a time, de-quantise, add bias, round, optional
-//               per-row sum of squares, 16-byte stores
+//   warps 2..9  epilogue (two warps per TMEM lane quarter, one per 128-column half of the tile):
+//               tcgen05.ld 32 columns at a time, de-quantise with scales staged in shared memory, add
+//               bias, round, optional per-row sum of squares per 128-column block, 16-byte stores
 // Tiles are visited column-block-fastest so that the CTAs of one wave share the same rows of qx
 // in L2 while the (much smaller) weight matrix stays L2-resident.
 #include "common.cuh"
@@ -25,8 +26,9 @@ constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BKB;
 constexpr int B_BYTES = BN * BKB;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int GEMM_THREADS = 192;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int GEMM_THREADS = 320;     // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
+constexpr int EPI_THREADS = 256;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + 8 * 2 * 128 * 4 /*per-warp sw, bias*/;
 
 struct GemmParams {
   const float* sx;
@@ -38,7 +40,7 @@ struct GemmParams {
   int* status;
   int64_t M, N, K, ldo, out_col_group, out_group_stride;
   int m_tiles, n_tiles, k_blocks;
-  int bias_dtype, out_dtype;
+  int bias_dtype;
 };
 
 __device__ __forceinline__ float load_as_float(const void* p, int dt, int64_t i) {
@@ -47,13 +49,28 @@ __device__ __forceinline__ float load_as_float(const void* p, int dt, int64_t i)
   return static_cast<const float*>(p)[i];
 }
 
-__device__ __forceinline__ float round_to(float v, int dt) {
-  if (dt == DAX_BF16) return __bfloat162float(__float2bfloat16_rn(v));
-  if (dt == DAX_F16) return __half2float(__float2half_rn(v));
-  return v;
+// Round a pair to the output dtype; returns the packed 16-bit pair and leaves the rounded values in a, b.
+template <int OUT>
+__device__ __forceinline__ uint32_t round_pair(float& a, float& b) {
+  if constexpr (OUT == DAX_BF16) {
+    uint32_t pk;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(pk) : "f"(b), "f"(a));
+    a = __uint_as_float(pk << 16);
+    b = __uint_as_float(pk & 0xffff0000u);
+    return pk;
+  } else if constexpr (OUT == DAX_F16) {
+    uint32_t pk;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(pk) : "f"(b), "f"(a));
+    const __half2 h = *reinterpret_cast<__half2*>(&pk);
+    a = __low2float(h);
+    b = __high2float(h);
+    return pk;
+  } else {
+    return 0;
+  }
 }
 
-template <int KIND>
+template <int KIND, int OUT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_dequant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GemmParams p, const uint32_t idesc) {
@@ -66,6 +83,7 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   uint64_t* acc_empty = acc_full + 2;     // [2] epilogue -> MMA
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  float* scale_stage = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256);  // [8 warps][sw 128 | bias 128]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -77,7 +95,7 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&acc_full[i], 1);
-      mbar_init(&acc_empty[i], 4);  // one arrival per epilogue warp
+      mbar_init(&acc_empty[i], EPI_THREADS / 32);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -146,8 +164,10 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
-    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32) belong to this warp
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    // warp -> TMEM lane quarter (warp % 4, fixed by the hardware) and column half of the 256-wide tile
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     uint32_t local_tile = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local_tile) {
@@ -156,18 +176,35 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int n_blk = tile % p.n_tiles;
       const int64_t m0 = static_cast<int64_t>(tile / p.n_tiles) * BM;
       const int64_t n0 = static_cast<int64_t>(n_blk) * BN;
+      // stage the weight scales and bias (as fp32) of this warp's 128 columns in its own slice of
+      // shared memory: no cross-warp synchronisation, so no warp can be left waiting at a barrier
+      float* swp_w = scale_stage + (warp - 2) * 256;
+      float* bp_w = swp_w + 128;
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int cl = lane + 32 * i;
+        const int64_t col = n0 + half * (BN / 2) + cl;
+        const bool col_ok = col < p.N;
+        swp_w[cl] = col_ok ? __ldg(p.sw + col) : 0.f;
+        bp_w[cl] = (col_ok && p.bias != nullptr) ? load_as_float(p.bias, p.bias_dtype, col) : 0.f;
+      }
+      __syncwarp();
       if (!mbar_wait(&acc_full[buf], use & 1u, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
       const int64_t row = m0 + quarter * 32 + lane;
       const bool row_ok = row < p.M;
       const float sx = row_ok ? p.sx[row] : 0.f;
+      const bool has_bias = p.bias != nullptr;
+      const bool want_ss = p.row_sumsq != nullptr;
       float sumsq = 0.f;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < BN / 64; ++c) {
+        const int cl = half * (BN / 2) + c * 32;  // column inside the tile
         uint32_t r[32];
-        tmem_ld32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN + c * 32, r);
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN + cl, r);
         tmem_wait_ld();
-        const int64_t col0 = n0 + c * 32;
+        const int64_t col0 = n0 + cl;
         if (col0 >= p.N) continue;
         if (p.acc_dump != nullptr && row_ok) {
           uint32_t* dump = static_cast<uint32_t*>(p.acc_dump) + row * p.N + col0;
@@ -175,32 +212,43 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           for (int j = 0; j < 32; ++j)
             if (col0 + j < p.N) dump[j] = r[j];
         }
+        const float* swp = swp_w + c * 32;
+        const float* bp = bp_w + c * 32;
+        uint32_t packed[16];
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int64_t col = col0 + j;
-          const bool col_ok = col < p.N;
-          const float sw = col_ok ? __ldg(p.sw + col) : 0.f;
-          float a;
-          if constexpr (KIND == KIND_I8) a = __int2float_rn(static_cast<int>(r[j]));
-          else a = __uint_as_float(r[j]);
-          float t = __fmul_rn(__fmul_rn(a, sx), sw);
+        for (int j = 0; j < 32; j += 2) {
+          float a0, a1;
+          if constexpr (KIND == KIND_I8) {
+            a0 = __int2float_rn(static_cast<int>(r[j]));
+            a1 = __int2float_rn(static_cast<int>(r[j + 1]));
+          } else {
+            a0 = __uint_as_float(r[j]);
+            a1 = __uint_as_float(r[j + 1]);
+          }
+          float t0 = __fmul_rn(__fmul_rn(a0, sx), swp[j]);
+          float t1 = __fmul_rn(__fmul_rn(a1, sx), swp[j + 1]);
           if constexpr (KIND == KIND_I8) {
             // reference order: cast to the output dtype, then add the bias in the output dtype
-            t = round_to(t, p.out_dtype);
-            if (p.bias != nullptr && col_ok) t = round_to(__fadd_rn(t, load_as_float(p.bias, p.bias_dtype, col)), p.out_dtype);
+            packed[j / 2] = round_pair<OUT>(t0, t1);
+            if (has_bias) {
+              t0 = __fadd_rn(t0, bp[j]);
+              t1 = __fadd_rn(t1, bp[j + 1]);
+              packed[j / 2] = round_pair<OUT>(t0, t1);
+            }
           } else {
-            // scaled-matmul semantics: bias joins in fp32, one rounding
-            if (p.bias != nullptr && col_ok) t = __fadd_rn(t, load_as_float(p.bias, p.bias_dtype, col));
-            t = round_to(t, p.out_dtype);
+            // scaled-matmul semantics: the bias joins in fp32, one rounding
+            t0 = __fadd_rn(t0, bp[j]);
+            t1 = __fadd_rn(t1, bp[j + 1]);
+            packed[j / 2] = round_pair<OUT>(t0, t1);
           }
-          v[j] = t;
-          sumsq = fmaf(t, t, sumsq);
+          if (want_ss) sumsq = fmaf(t1, t1, fmaf(t0, t0, sumsq));
+          if constexpr (OUT == DAX_F32) { v[j] = t0; v[j + 1] = t1; }
         }
         if (row_ok) {
           const int64_t g = col0 / p.out_col_group;
           const int64_t off = g * p.out_group_stride + row * p.ldo + (col0 - g * p.out_col_group);
-          if (p.out_dtype == DAX_F32) {
+          if constexpr (OUT == DAX_F32) {
             float* o = static_cast<float*>(p.out) + off;
 #pragma unroll
             for (int j = 0; j < 32; j += 4)
@@ -208,24 +256,9 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           } else {
             uint16_t* o = static_cast<uint16_t*>(p.out) + off;
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (col0 + j < p.N) {
-                uint32_t w[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  uint16_t lo, hi;
-                  if (p.out_dtype == DAX_BF16) {
-                    lo = __bfloat16_as_ushort(__float2bfloat16_rn(v[j + 2 * q]));
-                    hi = __bfloat16_as_ushort(__float2bfloat16_rn(v[j + 2 * q + 1]));
-                  } else {
-                    lo = __half_as_ushort(__float2half_rn(v[j + 2 * q]));
-                    hi = __half_as_ushort(__float2half_rn(v[j + 2 * q + 1]));
-                  }
-                  w[q] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
-                }
-                *reinterpret_cast<uint4*>(o + j) = make_uint4(w[0], w[1], w[2], w[3]);
-              }
-            }
+            for (int j = 0; j < 32; j += 8)
+              if (col0 + j < p.N)
+                *reinterpret_cast<uint4*>(o + j) = make_uint4(packed[j / 2], packed[j / 2 + 1], packed[j / 2 + 2], packed[j / 2 + 3]);
           }
         }
       }
@@ -233,7 +266,7 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
-      if (p.row_sumsq != nullptr && row_ok) p.row_sumsq[row * p.n_tiles + n_blk] = sumsq;
+      if (want_ss && row_ok) p.row_sumsq[row * (2 * p.n_tiles) + 2 * n_blk + half] = sumsq;
     }
   }
 
@@ -244,6 +277,23 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tmem_dealloc(tmem_base, 512);
   }
   if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, DAX_ERR_TIMEOUT);
+}
+
+template <int KIND, int OUT>
+int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams& p, uint32_t idesc, int grid,
+                cudaStream_t st) {
+  DAX_CUDA(cudaFuncSetAttribute(gemm_dequant_kernel<KIND, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  gemm_dequant_kernel<KIND, OUT><<<grid, GEMM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p, idesc);
+  DAX_CUDA(cudaGetLastError());
+  return DAX_OK;
+}
+
+template <int KIND>
+int launch_gemm_out(int out_dtype, const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams& p,
+                    uint32_t idesc, int grid, cudaStream_t st) {
+  if (out_dtype == DAX_BF16) return launch_gemm<KIND, DAX_BF16>(map_a, map_b, p, idesc, grid, st);
+  if (out_dtype == DAX_F16) return launch_gemm<KIND, DAX_F16>(map_a, map_b, p, idesc, grid, st);
+  return launch_gemm<KIND, DAX_F32>(map_a, map_b, p, idesc, grid, st);
 }
 
 bool is_f8(int dt) { return dt == DAX_E4M3 || dt == DAX_E5M2; }
@@ -303,31 +353,18 @@ extern "C" int dax_gemm_dequant(const void* qx, int a_dtype, const float* sx, co
   p.m_tiles = static_cast<int>((M + BM - 1) / BM);
   p.n_tiles = static_cast<int>((N + BN - 1) / BN);
   p.k_blocks = static_cast<int>((K + BKB - 1) / BKB);
-  p.bias_dtype = bias_dtype; p.out_dtype = out_dtype;
+  p.bias_dtype = bias_dtype;
   const int64_t total = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
   DAX_REQUIRE(total < (1ll << 31), DAX_ERR_UNSUPPORTED, "gemm_dequant: too many tiles");
   const int grid = static_cast<int>(total < sm_count() ? total : sm_count());
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
   if (i8) {
-    static bool attr_done = false;
-    if (!attr_done) {
-      DAX_CUDA(cudaFuncSetAttribute(gemm_dequant_kernel<KIND_I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-      attr_done = true;
-    }
     const uint32_t idesc = make_idesc(/*c=s32*/ 2, /*a=s8*/ 1, /*b=s8*/ 1, BM, BN);
-    gemm_dequant_kernel<KIND_I8><<<grid, GEMM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p, idesc);
-  } else {
-    static bool attr_done = false;
-    if (!attr_done) {
-      DAX_CUDA(cudaFuncSetAttribute(gemm_dequant_kernel<KIND_F8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-      attr_done = true;
-    }
-    const uint32_t idesc = make_idesc(/*c=f32*/ 1, a_dtype == DAX_E5M2 ? 1 : 0, b_dtype == DAX_E5M2 ? 1 : 0, BM, BN);
-    gemm_dequant_kernel<KIND_F8><<<grid, GEMM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p, idesc);
+    return launch_gemm_out<KIND_I8>(out_dtype, map_a, map_b, p, idesc, grid, st);
   }
-  DAX_CUDA(cudaGetLastError());
-  return DAX_OK;
+  const uint32_t idesc = make_idesc(/*c=f32*/ 1, a_dtype == DAX_E5M2 ? 1 : 0, b_dtype == DAX_E5M2 ? 1 : 0, BM, BN);
+  return launch_gemm_out<KIND_F8>(out_dtype, map_a, map_b, p, idesc, grid, st);
 }
 
 extern "C" int dax_gemm_i8_dequant(const void* qx, const float* sx, const void* qw, const float* sw, const void* bias,

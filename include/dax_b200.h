@@ -85,8 +85,9 @@ int dax_quant_rowwise(const void* x, int x_dtype, int64_t M, int64_t K, int64_t 
  *        With out_col_group = h*d and out_group_stride = s*h*d the projection writes straight into
  *        the send buffer [P, s, h, d] of the sequence->head exchange
  *        (dax/parallel/patches/wanx2_1_t2v_opt/layer.py:35-42,113-120).
- *   row_sumsq: optional [M, ceil(N/256)] fp32; slot (t, j) receives the sum of squares of the
- *        rounded outputs of row t in column tile j (feeds the RMSNorm that follows a Q/K projection).
+ *   row_sumsq: optional [M, 2*ceil(N/256)] fp32; slot (t, j) receives the sum of squares of the
+ *        rounded outputs of row t in columns [128 j, 128 j + 128) (feeds the RMSNorm that follows a
+ *        Q/K projection).
  *   acc_dump: optional [M, N] int32 (INT8) / fp32 (FP8) raw accumulators, for parity tests.
  * K % 16 == 0, N % 8 == 0, out_col_group % 32 == 0 (or == N), pointers 16-byte aligned.
  * The reference's float fallback for M <= 16 (linear.py:186-202) does not exist here.

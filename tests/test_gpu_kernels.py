@@ -108,7 +108,7 @@ def test_gemm_int8_bit_exact(ops, M, N, K, out_dtype):
     qw, sw = O.quantize_weight(w, torch.int8)
     yr, qx, sx, acc = O.linear_int8(x, qw, sw, b, out_dtype, return_parts=True)
     dump = torch.zeros(M, N, dtype=torch.int32, device=DEV)
-    ss = torch.zeros(M, (N + 255) // 256, device=DEV)
+    ss = torch.zeros(M, 2 * ((N + 255) // 256), device=DEV)
     y = ops.gemm_dequant(qx.to(DEV), sx.to(DEV), qw.to(DEV), sw.to(DEV).reshape(-1).contiguous(), b.to(DEV), out_dtype,
                          acc_dump=dump, row_sumsq=ss)
     assert torch.equal(dump.cpu(), acc), "int32 accumulators differ"
