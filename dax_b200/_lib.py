@@ -13,7 +13,7 @@ from .build import library_path
 
 DAX_OK, DAX_ERR_INVALID, DAX_ERR_ALIGN, DAX_ERR_UNSUPPORTED, DAX_ERR_CUDA, DAX_ERR_TIMEOUT = range(6)
 DAX_BF16, DAX_F16, DAX_F32, DAX_I8, DAX_E4M3, DAX_E5M2 = range(6)
-DAX_ATTN_QK_I8_PV_F8, DAX_ATTN_QK_F16_PV_F16 = 0, 1
+DAX_ATTN_QK_I8_PV_F8, DAX_ATTN_QK_BF16_PV_BF16, DAX_ATTN_QK_I8_PV_BF16 = 0, 1, 2
 
 I64x3 = c_int64 * 3
 

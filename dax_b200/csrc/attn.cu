@@ -2,21 +2,29 @@
 //
 // Two precisions of the two contractions (template parameters, chosen per call):
 //   INT8 Q.K^T (kind::i8, int32 accumulators)  + FP8 e4m3 P.V (kind::f8f6f4, fp32 accumulators)
-//   fp16 Q.K^T (kind::f16, fp32 accumulators)  + fp16 P.V
+//   bf16 Q.K^T (kind::f16, fp32 accumulators)  + bf16 P.V
+//   INT8 Q.K^T                                 + bf16 P.V   (V unquantised; P -> bf16 by truncation)
 // A CTA owns 256 query rows of one (batch, head): two 128-row tiles X = 0, 1 that ping-pong so
 // that the tensor pipe works on one tile while the softmax warps work on the other.
 //
-//   warps 0..3   softmax + correction + epilogue of tile 0 (thread = one query row)
-//   warps 4..7   the same for tile 1
-//   warp  8      TMA producer: both Q tiles once, then K_0, V_0, K_1, V_1, ... through a ring
-//   warp  9      MMA issuer (one thread)
+//   warps 0..7    softmax + correction + epilogue of tile 0: thread = one query row x 64 key columns
+//                 (warps w and w+4 share the rows of TMEM lane quarter w%4 and split the columns)
+//   warps 8..15   the same for tile 1
+//   warp  16      TMA producer: both Q tiles once, then K_0, V_0, K_1, V_1, ... through a ring
+//   warp  17      MMA issuer for Q.K^T of both tiles (one thread)
+//   warps 18, 19  MMA issuers for P.V of tile 0 / tile 1 (one thread each)
+// Four softmax warps per scheduler instead of two: the softmax is a chain of dependent fixed-latency
+// operations around a 16-per-clock exp unit, and only more resident warps hide that latency.  The two
+// threads of a row agree on the row maximum through a sequence-stamped shared-memory slot (no CTA or
+// named barrier, every poll is bounded) and add their partial row sums once at the end.
 //
 // Tensor memory (512 columns): S_0 [0,128)  S_1 [128,256)  O_0 [256,384)  O_1 [384,512).
 // Per KV tile j and query tile X:   S_X = Q_X . K_j^T   ->  softmax warps read S_X, keep the running
 // row maximum m and sum l (base-2 domain), write P_X to shared memory in the K-major 128-byte
 // swizzled layout the MMA reads, rescale O_X in tensor memory when m moved  ->  O_X += P_X . V_j.
-// A tcgen05.commit completes only after every earlier MMA of the issuing thread, so the arrival of
-// S_X(j+1) also tells the softmax warps that P_X . V_j is done: P_X may be overwritten and O_X rescaled.
+// The softmax warps copy S_X into registers first and release it at once (s_free), so Q_X . K_{j+1}^T
+// runs while they are still exponentiating tile j: they never wait for a score tile.  P_X and O_X are
+// reused only after P_X . V_{j-1} has completed (pv_done), which by then it normally has.
 //
 // Operands come from the workspace written by the prepare step (attn_prep.cu): every tile is a set
 // of [128 rows x 128 bytes] boxes, so one shared-memory descriptor form serves Q, K, P and V^T.
@@ -28,7 +36,20 @@
 namespace dax {
 namespace {
 
-constexpr int ATT_THREADS = 320;
+#ifdef DAX_ATTN_PROFILE
+// Phase timing for kernel tuning: compiled only when the macro is given on the command line.
+__device__ unsigned long long g_attn_prof[16];
+#define PROF_DECL unsigned long long prof_t0 = clock64(), prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define PROF_MARK(i) do { unsigned long long t_ = clock64(); prof_acc[i] += t_ - prof_t0; prof_t0 = t_; } while (0)
+#define PROF_FLUSH() do { if (blockIdx.x == 3 && blockIdx.y == 0 && warp == 5 && lane == 0) { for (int i_ = 0; i_ < 8; ++i_) g_attn_prof[i_] = prof_acc[i_]; g_attn_prof[8] = n_kv; } } while (0)
+#else
+#define PROF_DECL
+#define PROF_MARK(i)
+#define PROF_FLUSH()
+#endif
+
+constexpr int ATT_THREADS = 640;
+constexpr int SOFTMAX_WARPS = 16;
 constexpr int BOX_BYTES = 128 * 128;  // one [128 x 128 B] box
 
 template <int MODE> struct AttnCfg;
@@ -39,11 +60,18 @@ template <> struct AttnCfg<DAX_ATTN_QK_I8_PV_F8> {
   static constexpr float TAU = 0.f;          // P is scaled to the e4m3 range: the row max must be exact
   static constexpr float PBIAS = 8.8073549f; // log2(448): P in (0, 448]
 };
-template <> struct AttnCfg<DAX_ATTN_QK_F16_PV_F16> {
+template <> struct AttnCfg<DAX_ATTN_QK_BF16_PV_BF16> {
   static constexpr int QK_KIND = KIND_F16, PV_KIND = KIND_F16;
   static constexpr int EQ = 2, EP = 2;
-  static constexpr int NSLOT = 3;
-  static constexpr float TAU = 8.f;          // lazy rescale: P <= 2^8 fits fp16 easily
+  static constexpr int NSLOT = 2;            // 2 x 32 KB: shared memory is full (Q 64 KB + P 64 KB + ring 64 KB)
+  static constexpr float TAU = 8.f;          // lazy rescale: P <= 2^8, far inside the bf16 range
+  static constexpr float PBIAS = 0.f;
+};
+template <> struct AttnCfg<DAX_ATTN_QK_I8_PV_BF16> {
+  static constexpr int QK_KIND = KIND_I8, PV_KIND = KIND_F16;
+  static constexpr int EQ = 1, EP = 2;
+  static constexpr int NSLOT = 3;            // 3 x 32 KB (K tiles use half a slot): Q 32 KB + P 64 KB + ring 96 KB
+  static constexpr float TAU = 8.f;
   static constexpr float PBIAS = 0.f;
 };
 
@@ -58,7 +86,8 @@ struct Smem {
   static constexpr int OFF_RING = OFF_P + 2 * P_TILE;
   static constexpr int OFF_BAR = OFF_RING + C::NSLOT * SLOT;
   static constexpr int OFF_VSCALE = OFF_BAR + 256;
-  static constexpr int TOTAL = OFF_VSCALE + 512 + 1024 /*alignment slack*/;
+  static constexpr int OFF_XCHG = OFF_VSCALE + 512;           // [2 tiles][2 parities][2 halves][128 rows] x 8 B
+  static constexpr int TOTAL = OFF_XCHG + 2 * 2 * 2 * 128 * 8 + 1024 /*alignment slack*/;
 };
 
 struct AttnParams {
@@ -93,35 +122,22 @@ __device__ __forceinline__ void mma_tile(uint32_t d_tmem, uint32_t a_addr, uint3
   }
 }
 
-__device__ __forceinline__ uint32_t pack_f16x2(float a, float b) {
+// Two fp32 values -> bf16x2 by keeping the upper halves (one byte-permute for two elements; the
+// rounding conversion instructions run on the 16-per-clock unit the exponentials already saturate).
+// Truncation lowers every P by 2^-9 on average; the epilogue multiplies O by (1 + 2^-9) to centre it.
+__device__ __forceinline__ uint32_t pack_bf16x2_trunc(float a, float b) {
   uint32_t r;
-  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(r) : "r"(__float_as_uint(a)), "r"(__float_as_uint(b)));
   return r;
 }
 __device__ __forceinline__ float ex2(float x) {
+#ifdef DAX_ATTN_X_NOEXP  // tuning experiment only: take the exponential unit out of the picture
+  return x * 0.001f + 1.0f;
+#else
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-}
-
-// Row maximum of the scaled scores.  The scale is positive, so for integer accumulators the maximum
-// is taken on the integers and scaled once.
-template <int MODE, bool FULL>
-__device__ __forceinline__ float row_max(const uint32_t (&sv)[128], float cmul, int valid) {
-  using C = AttnCfg<MODE>;
-  if constexpr (C::QK_KIND == KIND_I8) {
-    int imax[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN};
-#pragma unroll
-    for (int i = 0; i < 128; ++i)
-      if (FULL || i < valid) imax[i & 3] = max(imax[i & 3], static_cast<int>(sv[i]));
-    return static_cast<float>(max(max(imax[0], imax[1]), max(imax[2], imax[3]))) * cmul;
-  } else {
-    float fmx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-    for (int i = 0; i < 128; ++i)
-      if (FULL || i < valid) fmx[i & 3] = fmaxf(fmx[i & 3], __uint_as_float(sv[i]));
-    return fmaxf(fmaxf(fmx[0], fmx[1]), fmaxf(fmx[2], fmx[3])) * cmul;
-  }
+#endif
 }
 
 __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
@@ -131,12 +147,32 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
   return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
 }
 
-// p_i = 2^(s_i * cmul + off) for the row held in sv; converts to the P format, writes the row into
-// the K-major 128-byte-swizzled P tile and returns the fp32 row sum (four independent partial sums
-// keep the add chain short).
+// Maximum of the scaled scores over the 64 columns a thread owns.  The scale is positive, so for
+// integer accumulators the maximum is taken on the integers and scaled once.
 template <int MODE, bool FULL>
-__device__ __forceinline__ float exp_and_store(const uint32_t (&sv)[128], float cmul, float off, int valid,
-                                               uint8_t* p_tile, int r) {
+__device__ __forceinline__ float row_max64(const uint32_t (&sv)[64], float cmul, int valid) {
+  using C = AttnCfg<MODE>;
+  if constexpr (C::QK_KIND == KIND_I8) {
+    int imax[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN};
+#pragma unroll
+    for (int i = 0; i < 64; ++i)
+      if (FULL || i < valid) imax[i & 3] = max(imax[i & 3], static_cast<int>(sv[i]));
+    return static_cast<float>(max(max(imax[0], imax[1]), max(imax[2], imax[3]))) * cmul;
+  } else {
+    float fmx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+    for (int i = 0; i < 64; ++i)
+      if (FULL || i < valid) fmx[i & 3] = fmaxf(fmx[i & 3], __uint_as_float(sv[i]));
+    return fmaxf(fmaxf(fmx[0], fmx[1]), fmaxf(fmx[2], fmx[3])) * cmul;
+  }
+}
+
+// p_i = 2^(s_i * cmul + off) for the 64 columns held in sv (columns 64*half .. 64*half+63 of the tile);
+// converts to the P format, writes them into the K-major 128-byte-swizzled P tile and returns the
+// fp32 partial row sum (four independent partial sums keep the add chain short).
+template <int MODE, bool FULL>
+__device__ __forceinline__ float exp_and_store64(const uint32_t (&sv)[64], float cmul, float off, int valid,
+                                                 uint8_t* p_tile, int r, int half) {
   using C = AttnCfg<MODE>;
   // int -> float by the 1.5 * 2^23 bias trick (|acc| <= 127*127*128 < 2^22), folded into the FMA
   const float off2 = fmaf(-12582912.f, cmul, off);
@@ -148,39 +184,69 @@ __device__ __forceinline__ float exp_and_store(const uint32_t (&sv)[128], float 
   };
   float sum[4] = {0.f, 0.f, 0.f, 0.f};
   if constexpr (C::EP == 1) {
+    // one row of the P tile is 128 bytes: this thread owns 16-byte chunks 4*half .. 4*half+3
 #pragma unroll
-    for (int ck = 0; ck < 8; ++ck) {
+    for (int c = 0; c < 4; ++c) {
       float e[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        e[i] = pv(16 * ck + i);
+        e[i] = pv(16 * c + i);
         sum[i & 3] += e[i];
       }
       uint4 w;
+#ifdef DAX_ATTN_X_NOCVT  // tuning experiment only (wrong results): no FP8 conversion
+      w.x = __float_as_uint(e[0] + e[1] + e[2] + e[3]);
+      w.y = __float_as_uint(e[4] + e[5] + e[6] + e[7]);
+      w.z = __float_as_uint(e[8] + e[9] + e[10] + e[11]);
+      w.w = __float_as_uint(e[12] + e[13] + e[14] + e[15]);
+#else
       w.x = pack_e4m3x4(e[0], e[1], e[2], e[3]);
       w.y = pack_e4m3x4(e[4], e[5], e[6], e[7]);
       w.z = pack_e4m3x4(e[8], e[9], e[10], e[11]);
       w.w = pack_e4m3x4(e[12], e[13], e[14], e[15]);
+#endif
+      const int ck = 4 * half + c;
       *reinterpret_cast<uint4*>(p_tile + r * 128 + ((ck ^ (r & 7)) << 4)) = w;
     }
   } else {
+    // bf16 P: two 16 KB boxes of 64 key columns each; this thread owns one full 128-byte row of box `half`
 #pragma unroll
-    for (int ck = 0; ck < 16; ++ck) {
+    for (int c = 0; c < 8; ++c) {
       float e[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        e[i] = pv(8 * ck + i);
+        e[i] = pv(8 * c + i);
         sum[i & 3] += e[i];
       }
       uint4 w;
-      w.x = pack_f16x2(e[0], e[1]);
-      w.y = pack_f16x2(e[2], e[3]);
-      w.z = pack_f16x2(e[4], e[5]);
-      w.w = pack_f16x2(e[6], e[7]);
-      *reinterpret_cast<uint4*>(p_tile + (ck >> 3) * BOX_BYTES + r * 128 + (((ck & 7) ^ (r & 7)) << 4)) = w;
+      w.x = pack_bf16x2_trunc(e[0], e[1]);
+      w.y = pack_bf16x2_trunc(e[2], e[3]);
+      w.z = pack_bf16x2_trunc(e[4], e[5]);
+      w.w = pack_bf16x2_trunc(e[6], e[7]);
+      *reinterpret_cast<uint4*>(p_tile + half * BOX_BYTES + r * 128 + ((c ^ (r & 7)) << 4)) = w;
     }
   }
   return (sum[0] + sum[1]) + (sum[2] + sum[3]);
+}
+
+// Sequence-stamped exchange slot between the two threads of a row: {value, sequence number}.
+__device__ __forceinline__ void xchg_write(uint2* slot, float v, uint32_t seq) {
+  asm volatile("st.volatile.shared.v2.u32 [%0], {%1, %2};" ::"r"(smem_u32(slot)), "r"(__float_as_uint(v)), "r"(seq)
+               : "memory");
+}
+__device__ __forceinline__ bool xchg_read(const uint2* slot, uint32_t seq, float& v, volatile uint32_t* abort_flag) {
+  const uint32_t addr = smem_u32(slot);
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    uint32_t a, b;
+    asm volatile("ld.volatile.shared.v2.u32 {%0, %1}, [%2];" : "=r"(a), "=r"(b) : "r"(addr) : "memory");
+    if (b == seq) {
+      v = __uint_as_float(a);
+      return true;
+    }
+    if ((i & 255u) == 255u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
 }
 
 template <int MODE>
@@ -196,10 +262,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   uint64_t* kv_full = bars + 1;                  // [NSLOT]
   uint64_t* kv_empty = kv_full + C::NSLOT;       // [NSLOT]
   uint64_t* s_full = kv_empty + C::NSLOT;        // [2]
-  uint64_t* p_full = s_full + 2;                 // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(p_full + 2);
+  uint64_t* p_full = s_full + 2;                 // [2]  softmax -> MMA: P_X written, O_X rescaled
+  uint64_t* s_free = p_full + 2;                 // [2]  softmax -> MMA: S_X is in registers, may be overwritten
+  uint64_t* pv_done = s_free + 2;                // [2]  MMA -> softmax: P_X . V_j complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   float* vscale_s = reinterpret_cast<float*>(smem + L::OFF_VSCALE);
+  uint2* xchg = reinterpret_cast<uint2*>(smem + L::OFF_XCHG);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -213,17 +282,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     mbar_init(q_full, 1);
     for (int i = 0; i < C::NSLOT; ++i) {
       mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+      mbar_init(&kv_empty[i], 2);  // released by two MMA commits (one per query tile)
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 128);
+      mbar_init(&p_full[i], 256);
+      mbar_init(&s_free[i], 8);   // one arrival per softmax warp of the tile
+      mbar_init(&pv_done[i], 1);
     }
     *abort_flag = 0;
     mbar_fence_init();
   }
   if (threadIdx.x < 128) vscale_s[threadIdx.x] = p.v_scale[static_cast<int64_t>(bh) * 128 + threadIdx.x];
-  if (warp == 8) {
+  for (int i = threadIdx.x; i < 2 * 2 * 2 * 128; i += ATT_THREADS) xchg[i] = make_uint2(0u, 0u);
+  if (warp == SOFTMAX_WARPS) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -232,7 +304,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 8) {
+  if (warp == SOFTMAX_WARPS) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&map_q);
@@ -266,130 +338,167 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
       }
     }
-  } else if (warp == 9) {
-    // ---------------------------------------------------------------- MMA issuer
+  } else if (warp == SOFTMAX_WARPS + 1) {
+    // ---------------------------------------------------------------- MMA issuer: Q.K^T of both tiles
+    // Three issuer threads (this one and one per tile for P.V) so that a late softmax of one tile does
+    // not hold back work that is ready for the other: each thread only waits for its own inputs.
     if (lane == 0) {
-      constexpr uint32_t idesc_qk = C::QK_KIND == KIND_I8 ? make_idesc(2, 1, 1, 128, 128) : make_idesc(1, 0, 0, 128, 128);
-      constexpr uint32_t idesc_pv = make_idesc(1, 0, 0, 128, 128);  // e4m3 x e4m3 or f16 x f16 -> f32
+      // s8 x s8 -> s32, or bf16 x bf16 -> f32
+      constexpr uint32_t idesc_qk = C::QK_KIND == KIND_I8 ? make_idesc(2, 1, 1, 128, 128) : make_idesc(1, 1, 1, 128, 128);
       const uint32_t q_addr = smem_u32(smem + L::OFF_Q);
-      const uint32_t p_addr = smem_u32(smem + L::OFF_P);
       const uint32_t ring = smem_u32(smem + L::OFF_RING);
-      auto slot_of = [](uint32_t seq) { return seq % C::NSLOT; };
-      auto phase_of = [](uint32_t seq) { return (seq / C::NSLOT) & 1u; };
       bool ok = mbar_wait(q_full, 0, abort_flag);
-      if (ok) ok = mbar_wait(&kv_full[slot_of(0)], phase_of(0), abort_flag);
-      if (ok) {
-        tc_fence_after_sync();
+      for (int j = 0; ok && j < n_kv; ++j) {  // S_X(j) for both tiles
+        const uint32_t seq_k = 2 * j, slot = seq_k % C::NSLOT, ph = (seq_k / C::NSLOT) & 1u;
+        if (!mbar_wait(&kv_full[slot], ph, abort_flag)) { ok = false; break; }
         for (int x = 0; x < 2; ++x) {
-          mma_tile<C::QK_KIND, C::EQ>(tmem_base + x * 128, q_addr + x * L::Q_TILE, ring + slot_of(0) * L::SLOT, idesc_qk, false);
-          umma_commit(&s_full[x]);
-        }
-        umma_commit(&kv_empty[slot_of(0)]);
-      }
-      for (int j = 0; ok && j < n_kv; ++j) {
-        const uint32_t seq_v = 2 * j + 1, seq_k = 2 * j + 2;
-        const bool more = j + 1 < n_kv;
-        if (!mbar_wait(&kv_full[slot_of(seq_v)], phase_of(seq_v), abort_flag)) { ok = false; break; }
-        if (more && !mbar_wait(&kv_full[slot_of(seq_k)], phase_of(seq_k), abort_flag)) { ok = false; break; }
-        for (int x = 0; x < 2; ++x) {
-          if (!mbar_wait(&p_full[x], j & 1u, abort_flag)) { ok = false; break; }
+          // S_X(j-1) has been copied to registers by all eight warps of the tile
+          if (j > 0 && !mbar_wait(&s_free[x], (j - 1) & 1u, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
-          mma_tile<C::PV_KIND, C::EP>(tmem_base + 256 + x * 128, p_addr + x * L::P_TILE, ring + slot_of(seq_v) * L::SLOT,
-                                      idesc_pv, j > 0);
-          if (more)
-            mma_tile<C::QK_KIND, C::EQ>(tmem_base + x * 128, q_addr + x * L::Q_TILE, ring + slot_of(seq_k) * L::SLOT,
-                                        idesc_qk, false);
+          mma_tile<C::QK_KIND, C::EQ>(tmem_base + x * 128, q_addr + x * L::Q_TILE, ring + slot * L::SLOT, idesc_qk, false);
           umma_commit(&s_full[x]);
+          umma_commit(&kv_empty[slot]);  // two arrivals free the slot: one per tile
         }
-        if (!ok) break;
-        umma_commit(&kv_empty[slot_of(seq_v)]);
-        if (more) umma_commit(&kv_empty[slot_of(seq_k)]);
       }
     }
-  } else {
+  } else if (warp >= SOFTMAX_WARPS + 2) {
+    // ---------------------------------------------------------------- MMA issuer: P.V of tile x
+    if (lane == 0) {
+      const int x = warp - (SOFTMAX_WARPS + 2);
+      // e4m3 x e4m3 -> f32, or bf16 x bf16 -> f32
+      constexpr uint32_t idesc_pv = C::PV_KIND == KIND_F8 ? make_idesc(1, 0, 0, 128, 128) : make_idesc(1, 1, 1, 128, 128);
+      const uint32_t p_addr = smem_u32(smem + L::OFF_P) + x * L::P_TILE;
+      const uint32_t ring = smem_u32(smem + L::OFF_RING);
+      bool ok = true;
+      for (int j = 0; ok && j < n_kv; ++j) {
+        const uint32_t seq_v = 2 * j + 1, slot = seq_v % C::NSLOT, ph = (seq_v / C::NSLOT) & 1u;
+        if (!mbar_wait(&kv_full[slot], ph, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&p_full[x], j & 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        mma_tile<C::PV_KIND, C::EP>(tmem_base + 256 + x * 128, p_addr, ring + slot * L::SLOT, idesc_pv, j > 0);
+        umma_commit(&pv_done[x]);
+        umma_commit(&kv_empty[slot]);  // the other tile's issuer supplies the second arrival
+      }
+    }
+  } else if (warp < SOFTMAX_WARPS) {
     // ---------------------------------------------------------------- softmax / correction / epilogue
-    const int x = warp >> 2;          // query tile of this warpgroup
-    const int quarter = warp & 3;     // TMEM lanes [32*quarter, +32)
+    const int x = warp >> 3;            // query tile
+    const int quarter = warp & 3;       // TMEM lanes [32*quarter, +32)
+    const int half = (warp >> 2) & 1;   // key columns [64*half, +64) of every tile; O channels likewise
     const int r = quarter * 32 + lane;  // row inside the tile
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t s_tmem = tmem_base + lane_base + x * 128;
-    const uint32_t o_tmem = tmem_base + lane_base + 256 + x * 128;
+    const uint32_t s_tmem = tmem_base + lane_base + x * 128 + half * 64;
+    const uint32_t o_tmem = tmem_base + lane_base + 256 + x * 128 + half * 64;
     uint8_t* p_tile = smem + L::OFF_P + x * L::P_TILE;
+    // exchange slots: [tile][parity][half][row]
+    auto slot = [&](int parity, int hf) { return xchg + ((x * 2 + parity) * 2 + hf) * 128 + r; };
     const int q_row = q0 + x * 128 + r;
     const float sq = q_row < p.Sq ? p.q_scale[static_cast<int64_t>(bh) * p.Sq_pad + q_row] : 1.f;
     const float* ks = p.k_scale + static_cast<int64_t>(bh) * n_kv;
     float m = -INFINITY, l = 0.f;
     float ks_next = ks[0];
     bool ok = true;
+    PROF_DECL;
 
     for (int j = 0; j < n_kv; ++j) {
       const float kscale = ks_next;
       if (j + 1 < n_kv) ks_next = ks[j + 1];
+      PROF_MARK(7);
       if (!mbar_wait(&s_full[x], j & 1u, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
-      uint32_t sv[128];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[c * 32]));
+      PROF_MARK(0);
+      uint32_t sv[64];
+      tmem_ld32(s_tmem, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+      tmem_ld32(s_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
       tmem_wait_ld();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[x]);  // S_X is in registers: Q.K^T of the next tile may start
+      PROF_MARK(1);
 
       const float cmul = sq * kscale;
-      const int valid = p.Sk - j * 128;  // columns >= valid are padding (only in the last tile)
-      const bool full = valid >= 128;
-      const float mx = full ? row_max<MODE, true>(sv, cmul, valid) : row_max<MODE, false>(sv, cmul, valid);
+      const int valid = p.Sk - j * 128 - half * 64;  // columns >= valid are padding (only in the last tile)
+      const bool full = valid >= 64;
+      const float pm = full ? row_max64<MODE, true>(sv, cmul, valid) : row_max64<MODE, false>(sv, cmul, valid);
+#ifdef DAX_ATTN_X_NOXCHG  // tuning experiment only (wrong results): no exchange with the partner thread
+      float pm2 = pm;
+#else
+      xchg_write(slot(j & 1, half), pm, static_cast<uint32_t>(j + 1));
+      float pm2;
+      if (!xchg_read(slot(j & 1, half ^ 1), static_cast<uint32_t>(j + 1), pm2, abort_flag)) { ok = false; break; }
+#endif
+      PROF_MARK(2);
+      const float mx = fmaxf(pm, pm2);
       const float m_new = (mx > m + C::TAU) ? mx : m;
       const float alpha = ex2(m - m_new);  // m = -inf on the first tile -> 0
       const float off = C::PBIAS - m_new;
-      const float sum = full ? exp_and_store<MODE, true>(sv, cmul, off, valid, p_tile, r)
-                             : exp_and_store<MODE, false>(sv, cmul, off, valid, p_tile, r);
+      // P_X and O_X are free once P_X . V_{j-1} has completed
+      if (j > 0) {
+        if (!mbar_wait(&pv_done[x], (j - 1) & 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+      }
+      PROF_MARK(3);
+      const float sum = full ? exp_and_store64<MODE, true>(sv, cmul, off, valid, p_tile, r, half)
+                             : exp_and_store64<MODE, false>(sv, cmul, off, valid, p_tile, r, half);
       l = fmaf(l, alpha, sum);
       m = m_new;
+      PROF_MARK(4);
 
       // correction: O_X *= alpha when any row of this warp moved its maximum (P_X . V_{j-1} is complete)
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        uint32_t ov[64];
+        tmem_ld32(o_tmem, *reinterpret_cast<uint32_t(*)[32]>(&ov[0]));
+        tmem_ld32(o_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&ov[32]));
+        tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t ov[32];
-          tmem_ld32(o_tmem + c * 32, ov);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-          tmem_st32(o_tmem + c * 32, ov);
-        }
+        for (int i = 0; i < 64; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+        tmem_st32(o_tmem, *reinterpret_cast<uint32_t(*)[32]>(&ov[0]));
+        tmem_st32(o_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&ov[32]));
         tmem_wait_st();
       }
+      PROF_MARK(5);
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(&p_full[x]);
+      PROF_MARK(6);
     }
+    PROF_FLUSH();
 
-    if (ok && mbar_wait(&s_full[x], n_kv & 1u, abort_flag)) {
+    if (ok && mbar_wait(&pv_done[x], (n_kv - 1) & 1u, abort_flag)) {
       tc_fence_after_sync();
-      const float inv_l = 1.f / l;
-      const bool store = q_row < q_stop;
-      const int b = bh / p.heads, h = bh % p.heads;
-      uint16_t* orow = static_cast<uint16_t*>(p.o) + b * p.o_sb + h * p.o_sh + static_cast<int64_t>(q_row) * p.o_st;
+      // the two threads of a row hold partial sums of the same row: add them
+      xchg_write(slot(n_kv & 1, half), l, static_cast<uint32_t>(n_kv + 1));
+      float l2 = 0.f;
+      if (xchg_read(slot(n_kv & 1, half ^ 1), static_cast<uint32_t>(n_kv + 1), l2, abort_flag)) {
+        // bf16 P was truncated, not rounded: centre the result (see pack_bf16x2_trunc)
+        const float inv_l = (C::EP == 2 ? 1.001953125f : 1.f) / (l + l2);
+        const bool store = q_row < q_stop;
+        const int b = bh / p.heads, h = bh % p.heads;
+        uint16_t* orow = static_cast<uint16_t*>(p.o) + b * p.o_sb + h * p.o_sh + static_cast<int64_t>(q_row) * p.o_st + half * 64;
+        const float* vs = vscale_s + half * 64;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t ov[32];
-        tmem_ld32(o_tmem + c * 32, ov);
-        tmem_wait_ld();
-        if (store) {
+        for (int c = 0; c < 2; ++c) {
+          uint32_t ov[32];
+          tmem_ld32(o_tmem + c * 32, ov);
+          tmem_wait_ld();
+          if (store) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint32_t w[4];
+            for (int i = 0; i < 32; i += 8) {
+              uint32_t w[4];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const float a = __uint_as_float(ov[i + 2 * q]) * vscale_s[c * 32 + i + 2 * q] * inv_l;
-              const float bb = __uint_as_float(ov[i + 2 * q + 1]) * vscale_s[c * 32 + i + 2 * q + 1] * inv_l;
-              if (p.out_bf16) {
-                w[q] = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(a))) |
-                       (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(bb))) << 16);
-              } else {
-                w[q] = static_cast<uint32_t>(__half_as_ushort(__float2half_rn(a))) |
-                       (static_cast<uint32_t>(__half_as_ushort(__float2half_rn(bb))) << 16);
+              for (int q = 0; q < 4; ++q) {
+                const float a = __uint_as_float(ov[i + 2 * q]) * vs[c * 32 + i + 2 * q] * inv_l;
+                const float bb = __uint_as_float(ov[i + 2 * q + 1]) * vs[c * 32 + i + 2 * q + 1] * inv_l;
+                if (p.out_bf16) {
+                  w[q] = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(a))) |
+                         (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(bb))) << 16);
+                } else {
+                  w[q] = static_cast<uint32_t>(__half_as_ushort(__float2half_rn(a))) |
+                         (static_cast<uint32_t>(__half_as_ushort(__float2half_rn(bb))) << 16);
+                }
               }
+              *reinterpret_cast<uint4*>(orow + c * 32 + i) = make_uint4(w[0], w[1], w[2], w[3]);
             }
-            *reinterpret_cast<uint4*>(orow + c * 32 + i) = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
       }
@@ -398,7 +507,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == SOFTMAX_WARPS) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
@@ -439,6 +548,11 @@ int launch_fwd(const AttnWorkspace& ws, const AttnParams& p, int64_t BH, cudaStr
   return DAX_OK;
 }
 
+#ifdef DAX_ATTN_PROFILE
+}  // namespace
+unsigned long long (&prof_symbol())[16] { return g_attn_prof; }
+namespace {
+#endif
 }  // namespace
 }  // namespace dax
 
@@ -476,5 +590,12 @@ extern "C" int dax_attn_forward(void* o, int dtype, int64_t B, int64_t heads, in
   p.out_bf16 = dtype == DAX_BF16;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (mode == DAX_ATTN_QK_I8_PV_F8) return launch_fwd<DAX_ATTN_QK_I8_PV_F8>(ws, p, B * heads, st);
-  return launch_fwd<DAX_ATTN_QK_F16_PV_F16>(ws, p, B * heads, st);
+  if (mode == DAX_ATTN_QK_I8_PV_BF16) return launch_fwd<DAX_ATTN_QK_I8_PV_BF16>(ws, p, B * heads, st);
+  return launch_fwd<DAX_ATTN_QK_BF16_PV_BF16>(ws, p, B * heads, st);
 }
+
+#ifdef DAX_ATTN_PROFILE
+extern "C" int dax_attn_profile_read(unsigned long long* host16) {
+  return cudaMemcpyFromSymbol(host16, dax::prof_symbol(), sizeof(unsigned long long) * 16) == cudaSuccess ? 0 : 4;
+}
+#endif

@@ -1,9 +1,9 @@
 // Workspace shared by the two attention steps (prepare and forward).  The caller owns the memory;
 // this header only fixes where each array lives inside it.
 //
-//   q      [BH, Sq_pad, 128]   INT8 or fp16, softmax scale * log2(e) folded in (INT8: per-token scale)
-//   k      [BH, Sk_pad, 128]   INT8 or fp16, per-(batch, head, channel) sequence mean removed
-//   vt     [BH, 128, Sk_pad]   FP8 e4m3 or fp16, transposed so that tokens are contiguous
+//   q      [BH, Sq_pad, 128]   INT8 or bf16, softmax scale * log2(e) folded in (INT8: per-token scale)
+//   k      [BH, Sk_pad, 128]   INT8 or bf16, per-(batch, head, channel) sequence mean removed
+//   vt     [BH, 128, Sk_pad]   FP8 e4m3 or bf16, transposed so that tokens are contiguous
 //   q_scale[BH, Sq_pad]  k_scale[BH, Sk_pad/128]  v_scale[BH, 128]      fp32
 //   k_mean [BH, 128]           fp32
 //   part   [BH, chunks, 2, 128] fp32 partial column sums of K and column maxima of |V|
@@ -31,16 +31,20 @@ struct AttnWorkspace {
 
 inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 
+// bytes per element of the Q/K operands and of the P/V operands for a mode
+inline int attn_qk_bytes(int mode) { return mode == DAX_ATTN_QK_BF16_PV_BF16 ? 2 : 1; }
+inline int attn_pv_bytes(int mode) { return mode == DAX_ATTN_QK_I8_PV_F8 ? 1 : 2; }
+
 // Fills `ws`; with base == nullptr only the size is computed.
 inline int attn_workspace_layout(int64_t B, int64_t heads, int64_t Sq, int64_t Sk, int mode, void* base,
                                  size_t available, AttnWorkspace* ws) {
   DAX_REQUIRE(B > 0 && heads > 0 && Sq > 0 && Sk > 0, DAX_ERR_INVALID, "attention: bad shape B=%lld heads=%lld Sq=%lld Sk=%lld",
               (long long)B, (long long)heads, (long long)Sq, (long long)Sk);
-  DAX_REQUIRE(mode == DAX_ATTN_QK_I8_PV_F8 || mode == DAX_ATTN_QK_F16_PV_F16, DAX_ERR_UNSUPPORTED,
-              "attention: unknown mode %d", mode);
+  DAX_REQUIRE(mode == DAX_ATTN_QK_I8_PV_F8 || mode == DAX_ATTN_QK_BF16_PV_BF16 || mode == DAX_ATTN_QK_I8_PV_BF16,
+              DAX_ERR_UNSUPPORTED, "attention: unknown mode %d", mode);
   const int64_t BH = B * heads;
   DAX_REQUIRE(BH <= 65535, DAX_ERR_UNSUPPORTED, "attention: batch*heads=%lld exceeds 65535", (long long)BH);
-  const int eq = mode == DAX_ATTN_QK_I8_PV_F8 ? 1 : 2;
+  const int eq = attn_qk_bytes(mode), ev = attn_pv_bytes(mode);
   ws->Sq_pad = round_up(Sq, 256);
   ws->Sk_pad = round_up(Sk, 128);
   ws->chunks = (Sk + kStatChunk - 1) / kStatChunk;
@@ -55,7 +59,7 @@ inline int attn_workspace_layout(int64_t B, int64_t heads, int64_t Sq, int64_t S
   uint8_t* b = static_cast<uint8_t*>(base);
   const size_t o_q = take(static_cast<size_t>(BH) * ws->Sq_pad * 128 * eq);
   const size_t o_k = take(static_cast<size_t>(BH) * ws->Sk_pad * 128 * eq);
-  const size_t o_v = take(static_cast<size_t>(BH) * ws->Sk_pad * 128 * eq);
+  const size_t o_v = take(static_cast<size_t>(BH) * ws->Sk_pad * 128 * ev);
   const size_t o_qs = take(static_cast<size_t>(BH) * ws->Sq_pad * 4);
   const size_t o_ks = take(static_cast<size_t>(BH) * (ws->Sk_pad / 128) * 4);
   const size_t o_vs = take(static_cast<size_t>(BH) * 128 * 4);

@@ -1,13 +1,13 @@
-// Prepare step of the quantised attention: turns bf16/fp16 Q, K, V (any batch/head/token strides,
+// Prepare step of the quantised attention: turns bf16/bf16 Q, K, V (any batch/head/token strides,
 // channels contiguous) into the operand arrays of the forward kernel (layout in attn_common.cuh).
 // HBM-bound: every input element is read twice at most (statistics pass + quantise pass for K and
 // V, once for Q) and written once at 1 or 2 bytes.
 //
 //   1. colstats      partial per-channel sums of K and maxima of |V| over blocks of 512 tokens
 //   2. colstats_fin  K mean and V scale per (batch, head, channel); fixed summation order
-//   3. quant_q       per token: q * (sm_scale * log2 e) -> INT8 with a per-token scale (or fp16)
-//   4. quant_k       per block of 128 tokens: (k - mean) -> INT8 with one scale per block (or fp16)
-//   5. quant_v       per block of 128 tokens: v / scale[channel] -> FP8 e4m3 (or fp16), transposed
+//   3. quant_q       per token: q * (sm_scale * log2 e) -> INT8 with a per-token scale (or bf16)
+//   4. quant_k       per block of 128 tokens: (k - mean) -> INT8 with one scale per block (or bf16)
+//   5. quant_v       per block of 128 tokens: v / scale[channel] -> FP8 e4m3 (or bf16), transposed
 // Subtracting the K mean leaves softmax unchanged (it shifts every score of a row by the same
 // amount) and removes the channel offset that would otherwise eat the INT8 range.
 #include <type_traits>
@@ -112,8 +112,8 @@ quant_q_kernel(const uint16_t* __restrict__ q, Strides qs, int heads, int64_t Sq
     if (lane == 0) q_scale[row] = sc;
   } else {
     uint2 w;
-    w.x = static_cast<uint32_t>(__half_as_ushort(__float2half_rn(f[0]))) | (static_cast<uint32_t>(__half_as_ushort(__float2half_rn(f[1]))) << 16);
-    w.y = static_cast<uint32_t>(__half_as_ushort(__float2half_rn(f[2]))) | (static_cast<uint32_t>(__half_as_ushort(__float2half_rn(f[3]))) << 16);
+    w.x = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(f[0]))) | (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(f[1]))) << 16);
+    w.y = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(f[2]))) | (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(f[3]))) << 16);
     reinterpret_cast<uint2*>(static_cast<uint16_t*>(qo) + row * 128)[lane] = w;
     if (lane == 0) q_scale[row] = cscale;
   }
@@ -183,8 +183,8 @@ quant_k_kernel(const uint16_t* __restrict__ k, Strides ks, int heads, int64_t Sk
       uint32_t w[4];
 #pragma unroll
       for (int q = 0; q < 4; ++q)
-        w[q] = static_cast<uint32_t>(__half_as_ushort(__float2half_rn(f[vi * 8 + 2 * q]))) |
-               (static_cast<uint32_t>(__half_as_ushort(__float2half_rn(f[vi * 8 + 2 * q + 1]))) << 16);
+        w[q] = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(f[vi * 8 + 2 * q]))) |
+               (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(f[vi * 8 + 2 * q + 1]))) << 16);
       dst[vi] = make_uint4(w[0], w[1], w[2], w[3]);
     }
     if (threadIdx.x == 0) k_scale[static_cast<int64_t>(bh) * (Sk_pad / 128) + blockIdx.x] = 1.f;
@@ -216,13 +216,13 @@ quant_v_kernel(const uint16_t* __restrict__ v, Strides vs, int heads, int64_t Sk
         const int c = cg * 8 + j;
         const float x = t < Sk ? ld16<BF16>(raw.v[j]) * inv_s[c] : 0.f;
         if constexpr (F8) tile[c * PITCH + tl] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
-        else tile[c * PITCH + tl] = __half_as_ushort(__float2half_rn(x));
+        else tile[c * PITCH + tl] = __bfloat16_as_ushort(__float2bfloat16_rn(x));
       }
     }
   }
   __syncthreads();
   {
-    // each warp writes whole channel rows: 128 tokens = 128 B (fp8) or 256 B (fp16)
+    // each warp writes whole channel rows: 128 tokens = 128 B (fp8) or 256 B (bf16)
     const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
     for (int c = wrp; c < 128; c += 8) {
       OutT* dst = static_cast<OutT*>(vo) + (static_cast<int64_t>(bh) * 128 + c) * Sk_pad + tok0;
@@ -243,21 +243,21 @@ int run_prepare(const void* q, const void* k, const void* v, int64_t B, int64_t 
   const uint16_t* qp = static_cast<const uint16_t*>(q);
   const uint16_t* kp = static_cast<const uint16_t*>(k);
   const uint16_t* vp = static_cast<const uint16_t*>(v);
-  const bool sage = mode == DAX_ATTN_QK_I8_PV_F8;
+  const bool qk_i8 = attn_qk_bytes(mode) == 1, v_f8 = attn_pv_bytes(mode) == 1;
   const float cscale = sm_scale * 1.4426950408889634f;
   const unsigned bh = static_cast<unsigned>(BH);
   colstats_kernel<BF16><<<dim3(static_cast<unsigned>(ws.chunks), bh), 256, 0, st>>>(kp, vp, ks, vs, static_cast<int>(heads), Sk, ws.part, ws.chunks);
-  colstats_fin_kernel<<<bh, 128, 0, st>>>(ws.part, ws.chunks, Sk, sage ? 1 : 0, ws.k_mean, ws.v_scale);
+  colstats_fin_kernel<<<bh, 128, 0, st>>>(ws.part, ws.chunks, Sk, v_f8 ? 1 : 0, ws.k_mean, ws.v_scale);
   const dim3 gq(static_cast<unsigned>(ws.Sq_pad / 8), bh), gk(static_cast<unsigned>(ws.Sk_pad / 128), bh);
-  if (sage) {
+  if (qk_i8) {
     quant_q_kernel<BF16, true><<<gq, 256, 0, st>>>(qp, qs, static_cast<int>(heads), Sq, ws.Sq_pad, cscale, ws.q, ws.q_scale);
     quant_k_kernel<BF16, true><<<gk, 256, 0, st>>>(kp, ks, static_cast<int>(heads), Sk, ws.Sk_pad, ws.k_mean, ws.k, ws.k_scale);
-    quant_v_kernel<BF16, true><<<gk, 256, 0, st>>>(vp, vs, static_cast<int>(heads), Sk, ws.Sk_pad, ws.v_scale, ws.vt);
   } else {
     quant_q_kernel<BF16, false><<<gq, 256, 0, st>>>(qp, qs, static_cast<int>(heads), Sq, ws.Sq_pad, cscale, ws.q, ws.q_scale);
     quant_k_kernel<BF16, false><<<gk, 256, 0, st>>>(kp, ks, static_cast<int>(heads), Sk, ws.Sk_pad, ws.k_mean, ws.k, ws.k_scale);
-    quant_v_kernel<BF16, false><<<gk, 256, 0, st>>>(vp, vs, static_cast<int>(heads), Sk, ws.Sk_pad, ws.v_scale, ws.vt);
   }
+  if (v_f8) quant_v_kernel<BF16, true><<<gk, 256, 0, st>>>(vp, vs, static_cast<int>(heads), Sk, ws.Sk_pad, ws.v_scale, ws.vt);
+  else quant_v_kernel<BF16, false><<<gk, 256, 0, st>>>(vp, vs, static_cast<int>(heads), Sk, ws.Sk_pad, ws.v_scale, ws.vt);
   DAX_CUDA(cudaGetLastError());
   return DAX_OK;
 }

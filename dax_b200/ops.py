@@ -16,8 +16,11 @@ from ._lib import I64x3, check, load
 _DT = {torch.bfloat16: _lib.DAX_BF16, torch.float16: _lib.DAX_F16, torch.float32: _lib.DAX_F32,
        torch.int8: _lib.DAX_I8, torch.float8_e4m3fn: _lib.DAX_E4M3, torch.float8_e5m2: _lib.DAX_E5M2}
 
+# "sage": INT8 Q.K^T + FP8 P.V;  "bf16" (alias "f16"): bf16 contractions, the high-accuracy mode;
+# "int8_bf16": INT8 Q.K^T + bf16 P.V (V unquantised)
 ATTN_MODES = {"sage": _lib.DAX_ATTN_QK_I8_PV_F8, "int8_fp8": _lib.DAX_ATTN_QK_I8_PV_F8,
-              "f16": _lib.DAX_ATTN_QK_F16_PV_F16}
+              "bf16": _lib.DAX_ATTN_QK_BF16_PV_BF16, "f16": _lib.DAX_ATTN_QK_BF16_PV_BF16,
+              "int8_bf16": _lib.DAX_ATTN_QK_I8_PV_BF16}
 
 
 class _Trace:

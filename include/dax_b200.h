@@ -42,8 +42,10 @@ typedef enum {
 
 /* Precision of the two tensor-core contractions of the attention kernel. */
 typedef enum {
-  DAX_ATTN_QK_I8_PV_F8 = 0,  /* INT8 Q.K^T, FP8(e4m3) P.V  — the SageAttention2-style mode   */
-  DAX_ATTN_QK_F16_PV_F16 = 1 /* fp16 Q.K^T, fp16 P.V       — high-accuracy mode              */
+  DAX_ATTN_QK_I8_PV_F8 = 0,     /* INT8 Q.K^T, FP8(e4m3) P.V  — the SageAttention2-style mode                */
+  DAX_ATTN_QK_BF16_PV_BF16 = 1, /* bf16 Q.K^T, bf16 P.V       — high-accuracy mode                           */
+  DAX_ATTN_QK_I8_PV_BF16 = 2    /* INT8 Q.K^T, bf16 P.V       — V unquantised; P becomes bf16 by truncation,
+                                    which costs the softmax warps less than the conversion to FP8        */
 } dax_attn_mode;
 
 int dax_version(void);
@@ -172,8 +174,8 @@ int dax_rmsnorm_rope_pack(const void* x, int dtype, int64_t s, int64_t D, int64_
  * dimension is contiguous; dtype BF16 or F16.  Sq may differ from Sk.
  * Two steps share a caller-provided workspace (dax_attn_workspace_bytes):
  *   dax_attn_prepare   K: per-(batch, head, channel) mean over the sequence removed, then INT8 per
- *                      block of 128 tokens (or fp16); Q: softmax scale folded in, INT8 per token (or
- *                      fp16); V: FP8 e4m3 with a per-channel scale, stored transposed (or fp16).
+ *                      block of 128 tokens (or bf16); Q: softmax scale folded in, INT8 per token (or
+ *                      bf16); V: FP8 e4m3 with a per-channel scale, stored transposed (or bf16).
  *   dax_attn_forward   flash-style pass over the prepared operands for the query rows
  *                      [q_begin + r*range_stride, q_end + r*range_stride), r = 0 .. n_ranges-1
  *                      (one call per O-path micro-batch: the i-th slice of every destination rank's

@@ -232,11 +232,11 @@ def qkv(B, H, Sq, Sk, dtype=torch.bfloat16, offset=2.0, seed=0):
 
 @pytest.mark.parametrize("S", [1, 128, 256, 1000, 2049])
 def test_attention_high_accuracy_mode(ops, S):
-    """fp16 contractions: the tolerance stated for attention against fp32 SDPA,
+    """bf16 contractions: the tolerance stated for attention against fp32 SDPA,
     rel-L2 <= 1e-2 and cosine >= 0.999."""
     q, k, v = qkv(1, 3, S, S)
     ref = O.sdpa_fp32(q, k, v)
-    o = ops.attention(q.to(DEV), k.to(DEV), v.to(DEV), mode="f16").float().cpu()
+    o = ops.attention(q.to(DEV), k.to(DEV), v.to(DEV), mode="bf16").float().cpu()
     assert not torch.isnan(o).any()
     assert O.rel_l2(o, ref) <= 1e-2 and O.cosine(o, ref) >= 0.999
 
@@ -256,6 +256,19 @@ def test_attention_sage_mode(ops, S):
     assert O.rel_l2(o, model) <= 4e-2
 
 
+@pytest.mark.parametrize("S", [1, 128, 1000, 2049])
+def test_attention_int8_bf16_mode(ops, S):
+    """INT8 Q.K^T + bf16 P.V (V unquantised): the remaining error is the INT8 rounding of Q and K, about
+    1e-2 rel-L2 on Gaussian data (per-token Q scales, per-128-token K scales), cosine >= 0.9999."""
+    q, k, v = qkv(1, 3, S, S)
+    ref = O.sdpa_fp32(q, k, v)
+    o = ops.attention(q.to(DEV), k.to(DEV), v.to(DEV), mode="int8_bf16").float().cpu()
+    assert not torch.isnan(o).any()
+    assert O.cosine(o, ref) >= 0.9999 and O.rel_l2(o, ref) <= 2e-2
+    model = O.sage_attention_model(q, k, v, qk="int8", pv="f16")
+    assert O.rel_l2(o, model) <= 1e-2
+
+
 def test_attention_k_smoothing_matters(ops):
     """A large per-channel K offset (the case mean-smoothing exists for) must not hurt accuracy."""
     q, k, v = qkv(1, 2, 512, 512, offset=20.0)
@@ -264,9 +277,9 @@ def test_attention_k_smoothing_matters(ops):
     assert O.cosine(o, ref) >= 0.999
 
 
-@pytest.mark.parametrize("mode", ["sage", "f16"])
+@pytest.mark.parametrize("mode", ["sage", "bf16", "int8_bf16"])
 def test_attention_layouts_ranges_and_cross(ops, mode):
-    tol = 5e-2 if mode == "sage" else 1e-2
+    tol = {"sage": 5e-2, "bf16": 1e-2, "int8_bf16": 2e-2}[mode]
     # token-major memory ([B, S, H, d] viewed as [B, H, S, d]), fp16, batch 2, Sq != Sk
     q, k, v = qkv(2, 2, 300, 77, dtype=torch.float16)
     ref = O.sdpa_fp32(q, k, v)
@@ -298,7 +311,7 @@ def test_attention_rows_are_convex_combinations(ops):
     k = torch.randn(1, H, S, 128, generator=g).bfloat16().to(DEV)
     c = torch.randn(1, H, 1, 128, generator=g).bfloat16()
     v = c.expand(1, H, S, 128).contiguous().to(DEV)
-    for mode, tol in (("sage", 3e-2), ("f16", 4e-3)):
+    for mode, tol in (("sage", 3e-2), ("bf16", 6e-3), ("int8_bf16", 6e-3)):
         o = ops.attention(q, k, v, mode=mode).float().cpu()
         assert O.rel_l2(o, c.float().expand_as(o)) <= tol
     # and a slice of query rows against fp32 SDPA over the full key set
