@@ -20,7 +20,6 @@ import os
 import statistics
 import subprocess
 import sys
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -44,34 +43,37 @@ def flops_per_step(tokens: int = TOKENS) -> float:
 # ----------------------------------------------------------------------------------------------
 # clocks
 # ----------------------------------------------------------------------------------------------
-class ClockSampler(threading.Thread):
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+class ClockSampler:
+    """Samples SM clock and throttle reasons while the timed region runs: ONE long-lived `nvidia-smi -lms`
+    process (spawning a query per sample stalls kernel launches of short steps)."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        super().__init__(daemon=True)
-        self.index, self.samples, self._stop_evt = index, [], threading.Event()
+        self.index, self.proc = index, None
 
-    def run(self):
-        while not self._stop_evt.is_set():
-            try:
-                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.samples.append([f.strip() for f in out.split(",")])
-            except Exception:
-                pass
-            self._stop_evt.wait(0.2)
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "200"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
 
     def stop(self):
-        self._stop_evt.set()
-        self.join(timeout=6)
-        sm = [int(s[0]) for s in self.samples if s[0].isdigit()]
-        mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
+        samples = []
+        if self.proc is not None:
+            self.proc.terminate()  # the exact process started above
+            try:
+                out, _ = self.proc.communicate(timeout=5)
+                samples = [[f.strip() for f in ln.split(",")] for ln in out.splitlines() if ln.strip()]
+            except Exception:
+                self.proc.kill()
+        sm = [int(s[0]) for s in samples if s[0].isdigit()]
+        mx = [int(s[1]) for s in samples if len(s) > 1 and s[1].isdigit()]
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = [n for i, n in enumerate(names) if any(len(s) > 2 + i and s[2 + i].lower() == "active" for s in self.samples)]
+        reasons = [n for i, n in enumerate(names) if any(len(s) > 2 + i and s[2 + i].lower() == "active" for s in samples)]
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": reasons, "samples": len(sm)}
 
