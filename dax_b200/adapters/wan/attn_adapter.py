@@ -74,11 +74,15 @@ def _rope_tables(rotary_emb: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
 
 class DAXWanAttnProcessor2_0:
     def __init__(self, sp_size: int = 1, overlap_comm: bool = False, attention_mode: str = "sage",
-                 qkv_chunks: int = 4, o_micro_batches: int = 2):
+                 qkv_chunks: int = 4, o_micro_batches: int = 2, o_split: str = "auto"):
         """``sp_size`` / ``overlap_comm`` as in the reference.  ``attention_mode``: "sage" (INT8 Q.K^T,
         FP8 P.V) or "f16" (fp16 contractions).  ``qkv_chunks``: token chunks of the Q/K/V projections
         whose exchange overlaps the next chunk's GEMMs; ``o_micro_batches``: micro-batches of the O
-        path (2 in the reference)."""
+        path (2 in the reference); ``o_split``: how the O path is cut, "rows" (the reference's scheme),
+        "ranks" (by groups of destination ranks) or "auto" (whichever needs fewer rounds of attention CTAs)."""
+        if o_split not in ("auto", "rows", "ranks"):
+            raise ValueError("o_split must be 'auto', 'rows' or 'ranks'")
+        self.o_split = o_split
         if attention_mode not in ops.ATTN_MODES:
             raise ValueError(f"attention_mode must be one of {sorted(ops.ATTN_MODES)}")
         self.sp_size = sp_size
@@ -220,9 +224,42 @@ class DAXWanAttnProcessor2_0:
             self._project(o_lin, attn_out, pair, out=out, ldo=D, col_group=D, group_stride=0, row_sumsq=None)
             return out
 
-        # O path: attend micro-batch i, start its exchange, and project micro-batch i-1 meanwhile
+        # O path.  Two ways to cut it into micro-batches whose exchange overlaps the next one's attention:
+        #  "rows":  micro-batch i = the i-th slice of EVERY destination rank's token block (the reference's
+        #           scheme): the O projection of slice i-1 overlaps too;
+        #  "ranks": micro-batch g = the whole blocks of a GROUP of destination ranks: one contiguous query
+        #           range per launch, no partly filled tail tile per range.
+        # The attention launches dominate, and every CTA (256 query rows x all keys) takes the same time, so
+        # the split that needs fewer rounds of SM-count CTAs wins; ties go to the reference's scheme.
         m = self.o_micro_batches if overlap else 1
         mb = micro_batch_bounds(s, m)
+        strategy = "rows"
+        gb = micro_batch_bounds(P, min(m, P))
+        if overlap and m > 1 and self.o_split == "ranks":
+            strategy = "ranks"
+        elif overlap and m > 1 and P >= 2 * m and self.o_split == "auto":
+            sms = torch.cuda.get_device_properties(dev).multi_processor_count
+            tiles = lambda n: (n + 255) // 256
+            rounds_rows = sum(-(-(P * tiles(mb[i + 1] - mb[i]) * h) // sms) for i in range(m))
+            rounds_ranks = sum(-(-(tiles((gb[g + 1] - gb[g]) * s) * h) // sms) for g in range(m))
+            if rounds_ranks < rounds_rows:
+                strategy = "ranks"
+        if strategy == "ranks":
+            o_recv = _BUFFERS.get("o_recv_full", (P, s, hd), dt, dev)
+            mine, sends = None, []
+            for g in range(len(gb) - 1):
+                g0, g1 = gb[g], gb[g + 1]
+                ops.attn_forward(plan, bhsd(attn_out), q_begin=g0 * s, q_end=g1 * s)
+                work = xchg.heads_to_tokens_group(attn_out, o_recv, s, range(g0, g1), async_op=True)
+                if g0 <= rank < g1:
+                    mine = work
+                else:
+                    sends.append(work)
+            self._o_project(o_lin, (mine, o_recv, 0, s), out, P, hd, D)
+            for w in sends:
+                w.wait()  # sends of the other groups: attn_out is rewritten by the next layer
+            return out
+
         pending = []
         for i in range(m):
             b0, b1 = mb[i], mb[i + 1]

@@ -87,6 +87,24 @@ class UlyssesExchange:
         recv[r].copy_(src[r * s + b0:r * s + b1])
         return self._run(ops, async_op)
 
+    def heads_to_tokens_group(self, src: torch.Tensor, recv: torch.Tensor, s: int, dests, async_op: bool = False):
+        """The same exchange restricted to a group of destination ranks: every rank sends its heads of the
+        WHOLE token block of each rank in ``dests``; only the ranks in ``dests`` receive (into
+        ``recv [P, s, hd]``, slab p = rank p's heads for this rank's tokens)."""
+        P, r = self.P, self.rank
+        dests = list(dests)
+        ops = []
+        if r in dests:
+            for p in range(P):
+                if p != r:
+                    ops.append(dist.P2POp(dist.irecv, recv[p], self.global_ranks[p], self.group))
+        for j in dests:
+            if j != r:
+                ops.append(dist.P2POp(dist.isend, src[j * s:(j + 1) * s], self.global_ranks[j], self.group))
+        if r in dests:
+            recv[r].copy_(src[r * s:(r + 1) * s])
+        return self._run(ops, async_op)
+
 
 def chunk_bounds(n: int, chunks: int, align: int = 128) -> List[int]:
     """Boundaries of at most ``chunks`` row ranges covering ``[0, n)``, each (but the last) a

@@ -49,12 +49,14 @@ def _worker(rank, world, port, S, D, H, grid, q):
         x, rope = _inputs(S, D, grid)
         s = S // world
         outs = {}
-        for overlap in (False, True):
+        for overlap in (False, True, "ranks"):
             holder = torch.nn.Module()
             holder.blocks = torch.nn.ModuleList([_build(D, H, 3)])
             pipe = _Pipe(holder.to(dev))
-            optimize_pipe(pipe, sequence_parallel=True, compile=False, overlap_comm=overlap, int8_linear=True,
+            optimize_pipe(pipe, sequence_parallel=True, compile=False, overlap_comm=bool(overlap), int8_linear=True,
                           attention_mode="f16")
+            if overlap == "ranks":  # O path cut by groups of destination ranks instead of row slices
+                holder.blocks[0].processor.o_split = "ranks"
             y = holder.blocks[0](x[:, rank * s:(rank + 1) * s].to(dev), rotary_emb=rope.to(dev))
             torch.cuda.synchronize()
             outs[overlap] = y.float().cpu()

@@ -137,6 +137,13 @@ def case_zero_copy_chunks(rank, world):
             xc.heads_to_tokens(recv, slab, s, b0, b1, async_op=False)
             out[b0:b1] = slab.transpose(0, 1)
         assert torch.equal(out.reshape(1, s, H, d), O.collect_heads_ref(full, rank))
+        # heads -> tokens by groups of destination ranks
+        slab = torch.zeros(world, s, hd)
+        gb = micro_batch_bounds(world, 2)
+        works = [xc.heads_to_tokens_group(recv, slab, s, range(g0, g1), async_op=True) for g0, g1 in zip(gb, gb[1:])]
+        for w in works:
+            w.wait()
+        assert torch.equal(slab.transpose(0, 1).reshape(1, s, H, d), O.collect_heads_ref(full, rank))
 
 
 @pytest.mark.parametrize("world", [2, 4])
