@@ -27,6 +27,11 @@ SIGNATURES = {
     "dax_gemm_dequant": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
                                  c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p,
                                  c_void_p]),
+    "dax_gemm_dequant_ex": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
+                                    c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p,
+                                    c_int, c_void_p, c_int64, c_void_p, c_void_p]),
+    "dax_layernorm_modulate_quant": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
+                                             c_void_p, c_float, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p]),
     "dax_gemm_i8_dequant": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                     c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "dax_gemm_f8_dequant": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,

@@ -104,15 +104,19 @@ class DAXWanAttnProcessor2_0:
 
     @staticmethod
     def _project(lin: nn.Module, x_rows: torch.Tensor, q_pair, *, out: torch.Tensor, ldo: int, col_group: int,
-                 group_stride: int, row_sumsq: Optional[torch.Tensor]) -> None:
-        """``out <- lin(x_rows)`` in the (grouped) layout given by ldo / col_group / group_stride."""
+                 group_stride: int, row_sumsq: Optional[torch.Tensor], resid: Optional[torch.Tensor] = None,
+                 gate: Optional[torch.Tensor] = None) -> None:
+        """``out <- lin(x_rows)`` in the (grouped) layout given by ldo / col_group / group_stride; with
+        ``resid`` the gated residual ``out <- resid + gate * lin(x_rows)`` (fused into the GEMM epilogue)."""
         if isinstance(lin, QLinear):
             lin._check_supported()
             qx, sx = q_pair
             lin.forward_quantized(qx, sx, out=out, ldo=ldo, out_col_group=col_group,
-                                  out_group_stride=group_stride, row_sumsq=row_sumsq)
+                                  out_group_stride=group_stride, row_sumsq=row_sumsq, resid=resid, gate=gate)
         else:  # float projection: library GEMM, then a strided copy into the layout
             y = F.linear(x_rows, lin.weight, lin.bias)
+            if resid is not None:
+                y = (resid.float() + (y.float() * gate if gate is not None else y.float())).to(y.dtype)
             rows, N = y.shape
             dst = torch.as_strided(out, (N // col_group, rows, col_group), (group_stride, ldo, 1))
             dst.copy_(y.view(rows, N // col_group, col_group).transpose(0, 1))
@@ -153,7 +157,11 @@ class DAXWanAttnProcessor2_0:
         return attn.to_out[1](out)  # dropout (identity at inference), as in the reference
 
     # ------------------------------------------------------------------------------------------
-    def _self_attention(self, attn, x: torch.Tensor, rotary_emb: Optional[torch.Tensor]) -> torch.Tensor:
+    def _self_attention(self, attn, x: torch.Tensor, rotary_emb: Optional[torch.Tensor], prequant=None,
+                        resid: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``x [s, D]`` -> ``[s, D]``.  ``prequant = (codes, scales)`` of ``x`` when the caller has already
+        quantised it (the fused block does, inside its LayerNorm kernel); ``resid`` / ``gate``: the O projection
+        writes ``resid + gate * o`` instead of ``o``."""
         s, D = x.shape
         H = attn.heads
         dev, dt = x.device, x.dtype
@@ -186,7 +194,10 @@ class DAXWanAttnProcessor2_0:
             c0, c1 = bounds[c], bounds[c + 1]
             rows = c1 - c0
             x_rows = x[c0:c1]
-            pairs = self._quantize_for(lins, x_rows)
+            if prequant is not None:
+                pairs = [(prequant[0][c0:c1], prequant[1][c0:c1]) if isinstance(lin, QLinear) else None for lin in lins]
+            else:
+                pairs = self._quantize_for(lins, x_rows)
             for i, (lin, norm) in enumerate(zip(lins, norms)):
                 dst = send[i].view(P * s, hd)[c0:]  # row c0 of slab 0; slabs are s*hd apart
                 if i == 2 or (norm is None and cos is None):
@@ -221,7 +232,8 @@ class DAXWanAttnProcessor2_0:
         if P == 1:
             ops.attn_forward(plan, bhsd(attn_out))
             pair = self._quantize_for((o_lin,), attn_out)[0]
-            self._project(o_lin, attn_out, pair, out=out, ldo=D, col_group=D, group_stride=0, row_sumsq=None)
+            self._project(o_lin, attn_out, pair, out=out, ldo=D, col_group=D, group_stride=0, row_sumsq=None,
+                          resid=resid, gate=gate)
             return out
 
         # O path.  Two ways to cut it into micro-batches whose exchange overlaps the next one's attention:
@@ -255,7 +267,7 @@ class DAXWanAttnProcessor2_0:
                     mine = work
                 else:
                     sends.append(work)
-            self._o_project(o_lin, (mine, o_recv, 0, s), out, P, hd, D)
+            self._o_project(o_lin, (mine, o_recv, 0, s), out, P, hd, D, resid, gate)
             for w in sends:
                 w.wait()  # sends of the other groups: attn_out is rewritten by the next layer
             return out
@@ -270,27 +282,32 @@ class DAXWanAttnProcessor2_0:
             work = xchg.heads_to_tokens(attn_out, o_recv, s, b0, b1, async_op=overlap)
             pending.append((work, o_recv, b0, b1))
             if len(pending) > 1:
-                self._o_project(o_lin, pending.pop(0), out, P, hd, D)
+                self._o_project(o_lin, pending.pop(0), out, P, hd, D, resid, gate)
         while pending:
-            self._o_project(o_lin, pending.pop(0), out, P, hd, D)
+            self._o_project(o_lin, pending.pop(0), out, P, hd, D, resid, gate)
         return out
 
-    def _o_project(self, o_lin, item, out: torch.Tensor, P: int, hd: int, D: int) -> None:
+    def _o_project(self, o_lin, item, out: torch.Tensor, P: int, hd: int, D: int, resid=None, gate=None) -> None:
         work, o_recv, b0, b1 = item
         work.wait()
         n = b1 - b0
+        res = resid[b0:b1] if resid is not None else None
         if isinstance(o_lin, QLinear):
             o_lin._check_supported()
             # the quantiser reads the receive slabs [P, n, h*d] in place as a [n, D] matrix
             qx, sx = ops.quant_rowwise(o_recv, o_lin.input_dtype, col_group=hd, group_stride=n * hd, rows=n, cols=D,
                                        ldx=hd)
-            o_lin.forward_quantized(qx, sx, out=out[b0:b1], ldo=D)
+            o_lin.forward_quantized(qx, sx, out=out[b0:b1], ldo=D, resid=res, gate=gate)
         else:
             xm = o_recv.permute(1, 0, 2).reshape(n, D)
-            out[b0:b1] = F.linear(xm, o_lin.weight, o_lin.bias)
+            y = F.linear(xm, o_lin.weight, o_lin.bias)
+            if res is not None:
+                y = (res.float() + (y.float() * gate if gate is not None else y.float())).to(y.dtype)
+            out[b0:b1] = y
 
     # ------------------------------------------------------------------------------------------
-    def _cross_attention(self, attn, x: torch.Tensor, ctx: torch.Tensor) -> torch.Tensor:
+    def _cross_attention(self, attn, x: torch.Tensor, ctx: torch.Tensor, prequant=None,
+                         resid: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Cross-attention (``attn2``): queries are this rank's tokens, keys/values the replicated text
         context.  Every query row attends to the whole context locally, so nothing is exchanged; the
         reference exchanges Q/K/V/O here too and attends over P identical copies of the context,
@@ -305,7 +322,8 @@ class DAXWanAttnProcessor2_0:
         n_tiles = 2 * ((D + 255) // 256)  # sum-of-squares partials: one per 128 columns
         for lin, norm, src, dst in ((attn.to_q, attn.norm_q, x, q), (attn.to_k, attn.norm_k, ctx, k),
                                     (attn.to_v, None, ctx, v)):
-            pair = self._quantize_for((lin,), src)[0]
+            pair = prequant if (prequant is not None and src is x and isinstance(lin, QLinear)) else \
+                self._quantize_for((lin,), src)[0]
             if norm is None:
                 self._project(lin, src, pair, out=dst, ldo=D, col_group=D, group_stride=0, row_sumsq=None)
                 continue
@@ -326,7 +344,7 @@ class DAXWanAttnProcessor2_0:
         o_lin = attn.to_out[0]
         out = torch.empty((s, D), dtype=dt, device=dev)
         pair = self._quantize_for((o_lin,), o)[0]
-        self._project(o_lin, o, pair, out=out, ldo=D, col_group=D, group_stride=0, row_sumsq=None)
+        self._project(o_lin, o, pair, out=out, ldo=D, col_group=D, group_stride=0, row_sumsq=None, resid=resid)
         return out
 
 

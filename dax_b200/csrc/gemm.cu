@@ -28,7 +28,7 @@ constexpr int B_BYTES = BN * BKB;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int GEMM_THREADS = 320;     // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
 constexpr int EPI_THREADS = 256;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + 8 * 2 * 128 * 4 /*per-warp sw, bias*/;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + 8 * 3 * 128 * 4 /*per-warp sw, bias, gate*/;
 
 struct GemmParams {
   const float* sx;
@@ -41,6 +41,12 @@ struct GemmParams {
   int64_t M, N, K, ldo, out_col_group, out_group_stride;
   int m_tiles, n_tiles, k_blocks;
   int bias_dtype;
+  // optional post-operations on the rounded linear output y (16-bit outputs only):
+  //   act == 1: y = gelu_tanh(y);   resid != null: y = resid[t, n] + gate[n] * y   (fp32, then rounded)
+  int act;
+  const void* resid;
+  int64_t ldr;
+  const float* gate;
 };
 
 __device__ __forceinline__ float load_as_float(const void* p, int dt, int64_t i) {
@@ -70,7 +76,15 @@ __device__ __forceinline__ uint32_t round_pair(float& a, float& b) {
   }
 }
 
-template <int KIND, int OUT>
+// GELU, tanh form: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), hardware tanh approximation
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float u = 0.7978845608028654f * fmaf(0.044715f * x * x, x, x);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  return 0.5f * x * (1.f + t);
+}
+
+template <int KIND, int OUT, bool POST>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_dequant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GemmParams p, const uint32_t idesc) {
@@ -83,7 +97,7 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   uint64_t* acc_empty = acc_full + 2;     // [2] epilogue -> MMA
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
-  float* scale_stage = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256);  // [8 warps][sw 128 | bias 128]
+  float* scale_stage = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256);  // [8 warps][sw 128 | bias 128 | gate 128]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -178,8 +192,9 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int64_t n0 = static_cast<int64_t>(n_blk) * BN;
       // stage the weight scales and bias (as fp32) of this warp's 128 columns in its own slice of
       // shared memory: no cross-warp synchronisation, so no warp can be left waiting at a barrier
-      float* swp_w = scale_stage + (warp - 2) * 256;
+      float* swp_w = scale_stage + (warp - 2) * 384;
       float* bp_w = swp_w + 128;
+      float* gp_w = swp_w + 256;
       __syncwarp();
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -188,6 +203,7 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const bool col_ok = col < p.N;
         swp_w[cl] = col_ok ? __ldg(p.sw + col) : 0.f;
         bp_w[cl] = (col_ok && p.bias != nullptr) ? load_as_float(p.bias, p.bias_dtype, col) : 0.f;
+        if constexpr (POST) gp_w[cl] = (col_ok && p.gate != nullptr) ? __ldg(p.gate + col) : 1.f;
       }
       __syncwarp();
       if (!mbar_wait(&acc_full[buf], use & 1u, abort_flag)) { ok = false; break; }
@@ -243,6 +259,28 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             packed[j / 2] = round_pair<OUT>(t0, t1);
           }
           if (want_ss) sumsq = fmaf(t1, t1, fmaf(t0, t0, sumsq));
+          if constexpr (POST) {
+            if (p.act == 1) {
+              t0 = gelu_tanh(t0);
+              t1 = gelu_tanh(t1);
+              packed[j / 2] = round_pair<OUT>(t0, t1);
+            }
+            if (p.resid != nullptr && row_ok && col0 + j < p.N) {
+              const uint32_t rr = *reinterpret_cast<const uint32_t*>(static_cast<const uint16_t*>(p.resid) + row * p.ldr + col0 + j);
+              float r0, r1;
+              if constexpr (OUT == DAX_BF16) {
+                r0 = __uint_as_float(rr << 16);
+                r1 = __uint_as_float(rr & 0xffff0000u);
+              } else {
+                const __half2 h = *reinterpret_cast<const __half2*>(&rr);
+                r0 = __low2float(h);
+                r1 = __high2float(h);
+              }
+              t0 = fmaf(gp_w[c * 32 + j], t0, r0);
+              t1 = fmaf(gp_w[c * 32 + j + 1], t1, r1);
+              packed[j / 2] = round_pair<OUT>(t0, t1);
+            }
+          }
           if constexpr (OUT == DAX_F32) { v[j] = t0; v[j + 1] = t1; }
         }
         if (row_ok) {
@@ -279,13 +317,22 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, DAX_ERR_TIMEOUT);
 }
 
+template <int KIND, int OUT, bool POST>
+int launch_gemm_post(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams& p, uint32_t idesc, int grid,
+                     cudaStream_t st) {
+  DAX_CUDA(cudaFuncSetAttribute(gemm_dequant_kernel<KIND, OUT, POST>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  gemm_dequant_kernel<KIND, OUT, POST><<<grid, GEMM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p, idesc);
+  DAX_CUDA(cudaGetLastError());
+  return DAX_OK;
+}
+
 template <int KIND, int OUT>
 int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams& p, uint32_t idesc, int grid,
                 cudaStream_t st) {
-  DAX_CUDA(cudaFuncSetAttribute(gemm_dequant_kernel<KIND, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-  gemm_dequant_kernel<KIND, OUT><<<grid, GEMM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p, idesc);
-  DAX_CUDA(cudaGetLastError());
-  return DAX_OK;
+  if constexpr (OUT != DAX_F32) {
+    if (p.act != 0 || p.resid != nullptr) return launch_gemm_post<KIND, OUT, true>(map_a, map_b, p, idesc, grid, st);
+  }
+  return launch_gemm_post<KIND, OUT, false>(map_a, map_b, p, idesc, grid, st);
 }
 
 template <int KIND>
@@ -305,7 +352,22 @@ extern "C" int dax_gemm_dequant(const void* qx, int a_dtype, const float* sx, co
                                 const float* sw, const void* bias, int bias_dtype, void* out, int out_dtype,
                                 int64_t M, int64_t N, int64_t K, int64_t ldo, int64_t out_col_group,
                                 int64_t out_group_stride, float* row_sumsq, void* acc_dump, void* stream) {
+  return dax_gemm_dequant_ex(qx, a_dtype, sx, qw, b_dtype, sw, bias, bias_dtype, out, out_dtype, M, N, K, ldo,
+                             out_col_group, out_group_stride, row_sumsq, acc_dump, 0, nullptr, 0, nullptr, stream);
+}
+
+extern "C" int dax_gemm_dequant_ex(const void* qx, int a_dtype, const float* sx, const void* qw, int b_dtype,
+                                   const float* sw, const void* bias, int bias_dtype, void* out, int out_dtype,
+                                   int64_t M, int64_t N, int64_t K, int64_t ldo, int64_t out_col_group,
+                                   int64_t out_group_stride, float* row_sumsq, void* acc_dump, int act,
+                                   const void* resid, int64_t ldr, const float* gate, void* stream) {
   using namespace dax;
+  DAX_REQUIRE(act == 0 || act == 1, DAX_ERR_UNSUPPORTED, "gemm_dequant: unknown activation %d", act);
+  DAX_REQUIRE((act == 0 && resid == nullptr) || out_dtype != DAX_F32, DAX_ERR_UNSUPPORTED,
+              "gemm_dequant: activation / residual epilogues need a 16-bit output dtype");
+  DAX_REQUIRE(resid == nullptr || (ldr % 2 == 0 && (reinterpret_cast<uintptr_t>(resid) & 3u) == 0), DAX_ERR_ALIGN,
+              "gemm_dequant: resid must be 4-byte aligned with an even leading dimension");
+  DAX_REQUIRE(gate == nullptr || resid != nullptr, DAX_ERR_INVALID, "gemm_dequant: gate needs resid");
   DAX_REQUIRE(M >= 0 && N > 0 && K > 0, DAX_ERR_INVALID, "gemm_dequant: bad shape M=%lld N=%lld K=%lld",
               (long long)M, (long long)N, (long long)K);
   if (M == 0) return DAX_OK;
@@ -354,6 +416,7 @@ extern "C" int dax_gemm_dequant(const void* qx, int a_dtype, const float* sx, co
   p.n_tiles = static_cast<int>((N + BN - 1) / BN);
   p.k_blocks = static_cast<int>((K + BKB - 1) / BKB);
   p.bias_dtype = bias_dtype;
+  p.act = act; p.resid = resid; p.ldr = ldr; p.gate = gate;
   const int64_t total = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
   DAX_REQUIRE(total < (1ll << 31), DAX_ERR_UNSUPPORTED, "gemm_dequant: too many tiles");
   const int grid = static_cast<int>(total < sm_count() ? total : sm_count());

@@ -12,7 +12,7 @@
 //   FP8 : q = round_nearest_even_to_fp8(clamp(x / scale))   (true division)
 // All fp32 operations are the IEEE round-to-nearest intrinsics so that the compiler cannot
 // contract or approximate them.
-#include "common.cuh"
+#include "quant_common.cuh"
 
 namespace dax {
 namespace {
@@ -46,23 +46,6 @@ __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
-}
-
-template <int QDT>
-__device__ __forceinline__ uint8_t quant_one(float x, float scale, float inv_scale) {
-  if constexpr (QDT == DAX_I8) {
-    float r = rintf(__fmul_rn(x, inv_scale));
-    r = fminf(fmaxf(r, -128.f), 127.f);
-    return static_cast<uint8_t>(static_cast<int8_t>(static_cast<int>(r)));
-  } else if constexpr (QDT == DAX_E4M3) {
-    float r = __fdiv_rn(x, scale);
-    r = fminf(fmaxf(r, -448.f), 448.f);
-    return static_cast<uint8_t>(__nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E4M3));
-  } else {
-    float r = __fdiv_rn(x, scale);
-    r = fminf(fmaxf(r, -57344.f), 57344.f);
-    return static_cast<uint8_t>(__nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E5M2));
-  }
 }
 
 // TPR threads cooperate on one row; a CTA of kThreads handles kThreads / TPR rows.

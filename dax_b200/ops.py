@@ -27,7 +27,7 @@ class _Trace:
     """Optional launch accounting: number of library kernels launched and, when timing is on, CUDA
     events around each wrapper on the stream it launches on (used by the benchmark's roofline leg)."""
 
-    KERNELS_PER_CALL = {"linear_dynamic": 2, "quant_rowwise": 1, "gemm_dequant": 1, "rmsnorm_rope_pack": 1, "attn_prepare": 5, "attn_forward": 1}
+    KERNELS_PER_CALL = {"layernorm_modulate_quant": 1, "linear_dynamic": 2, "quant_rowwise": 1, "gemm_dequant": 1, "rmsnorm_rope_pack": 1, "attn_prepare": 5, "attn_forward": 1}
 
     def __init__(self):
         self.launches = 0
@@ -113,8 +113,11 @@ def quant_rowwise(x: torch.Tensor, q_dtype: torch.dtype, *, col_group: Optional[
 def gemm_dequant(qx: torch.Tensor, sx: torch.Tensor, qw: torch.Tensor, sw: torch.Tensor,
                  bias: Optional[torch.Tensor], out_dtype: torch.dtype, *, out: Optional[torch.Tensor] = None,
                  ldo: Optional[int] = None, out_col_group: Optional[int] = None, out_group_stride: int = 0,
-                 row_sumsq: Optional[torch.Tensor] = None, acc_dump: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``out = cast((acc(qx @ qw.T) * sx) * sw) + bias`` on the tcgen05 INT8 / FP8 pipe."""
+                 row_sumsq: Optional[torch.Tensor] = None, acc_dump: Optional[torch.Tensor] = None,
+                 act: Optional[str] = None, resid: Optional[torch.Tensor] = None,
+                 gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out = cast((acc(qx @ qw.T) * sx) * sw) + bias`` on the tcgen05 INT8 / FP8 pipe, optionally followed
+    by ``act="gelu_tanh"`` and / or the gated residual ``out = resid + gate * out`` (gate ``[N]`` fp32)."""
     _need_cuda(qx, sx, qw, sw, bias, out)
     M, K = qx.shape
     N = qw.shape[0]
@@ -125,11 +128,18 @@ def gemm_dequant(qx: torch.Tensor, sx: torch.Tensor, qw: torch.Tensor, sw: torch
         ldo = N
     if out_col_group is None:
         out_col_group = N
+    if act not in (None, "gelu_tanh"):
+        raise NotImplementedError(f"unknown activation {act!r}")
+    if resid is not None:
+        _need_cuda(resid, gate)
+        assert resid.dtype == out_dtype and resid.stride(-1) == 1 and resid.shape == (M, N)
+        assert gate is None or (gate.dtype == torch.float32 and gate.numel() == N and gate.is_contiguous())
     tok = TRACE.begin("gemm_dequant")
-    check(load().dax_gemm_dequant(qx.data_ptr(), _dt(qx.dtype), sx.data_ptr(), qw.data_ptr(), _dt(qw.dtype),
-                                  sw.data_ptr(), _ptr(bias), _dt(bias.dtype) if bias is not None else 0,
-                                  out.data_ptr(), _dt(out_dtype), M, N, K, ldo, out_col_group, out_group_stride,
-                                  _ptr(row_sumsq), _ptr(acc_dump), _stream()))
+    check(load().dax_gemm_dequant_ex(qx.data_ptr(), _dt(qx.dtype), sx.data_ptr(), qw.data_ptr(), _dt(qw.dtype),
+                                     sw.data_ptr(), _ptr(bias), _dt(bias.dtype) if bias is not None else 0,
+                                     out.data_ptr(), _dt(out_dtype), M, N, K, ldo, out_col_group, out_group_stride,
+                                     _ptr(row_sumsq), _ptr(acc_dump), 1 if act else 0, _ptr(resid),
+                                     resid.stride(0) if resid is not None else 0, _ptr(gate), _stream()))
     TRACE.end(tok, (M, N, K))
     return out
 
@@ -153,6 +163,30 @@ def linear_dynamic(x: torch.Tensor, qw: torch.Tensor, sw: torch.Tensor, bias: Op
                                     ws.data_ptr() + off, n, _stream()))
     TRACE.end(tok, (M, N, K))
     return out
+
+
+def layernorm_modulate_quant(x: torch.Tensor, *, eps: float = 1e-6, ln_weight: Optional[torch.Tensor] = None,
+                             ln_bias: Optional[torch.Tensor] = None, shift: Optional[torch.Tensor] = None,
+                             scale: Optional[torch.Tensor] = None, q_dtype: Optional[torch.dtype] = None,
+                             want_y: bool = True):
+    """``y = LN(x) [* w + b] [* (1 + scale) + shift]`` per token row of ``x [s, D]`` (all vectors ``[D]`` fp32),
+    optionally with the per-token quantisation of ``y`` fused in.  Returns ``(y or None, q or None, qscale or None)``."""
+    _need_cuda(x, ln_weight, ln_bias, shift, scale)
+    s_, D = x.shape
+    assert x.stride(1) == 1
+    for v in (ln_weight, ln_bias, shift, scale):
+        assert v is None or (v.dtype == torch.float32 and v.numel() == D and v.is_contiguous())
+    y = torch.empty((s_, D), dtype=x.dtype, device=x.device) if want_y else None
+    q = qs = None
+    if q_dtype is not None:
+        q = torch.empty((s_, D), dtype=q_dtype, device=x.device)
+        qs = torch.empty((s_, 1), dtype=torch.float32, device=x.device)
+    tok = TRACE.begin("layernorm_modulate_quant")
+    check(load().dax_layernorm_modulate_quant(x.data_ptr(), _dt(x.dtype), s_, D, x.stride(0), _ptr(ln_weight),
+                                              _ptr(ln_bias), _ptr(shift), _ptr(scale), float(eps), _ptr(y), D, _ptr(q),
+                                              _dt(q_dtype) if q_dtype is not None else 0, _ptr(qs), _stream()))
+    TRACE.end(tok, (s_, D))
+    return y, q, qs
 
 
 def rmsnorm_rope_pack(x: torch.Tensor, *, norm_weight: Optional[torch.Tensor], do_norm: bool, eps: float = 1e-6,

@@ -99,6 +99,17 @@ int dax_gemm_dequant(const void* qx, int a_dtype, const float* sx, const void* q
                      int64_t N, int64_t K, int64_t ldo, int64_t out_col_group, int64_t out_group_stride,
                      float* row_sumsq, void* acc_dump, void* stream);
 
+/* dax_gemm_dequant with an epilogue for the rest of the DiT block (16-bit outputs only).  With y the
+ * rounded linear output:  act = 1: y <- gelu_tanh(y) (the FFN's first linear);  resid != NULL:
+ * out[t, n] = resid[t, n] + gate[n] * y (fp32, rounded once; gate NULL = 1): the gated residual that
+ * follows the O projection and the FFN's second linear in a Wan block.  resid is [M, N] (ldr) of out_dtype
+ * and may alias out.  Everything else as dax_gemm_dequant. */
+int dax_gemm_dequant_ex(const void* qx, int a_dtype, const float* sx, const void* qw, int b_dtype,
+                        const float* sw, const void* bias, int bias_dtype, void* out, int out_dtype, int64_t M,
+                        int64_t N, int64_t K, int64_t ldo, int64_t out_col_group, int64_t out_group_stride,
+                        float* row_sumsq, void* acc_dump, int act, const void* resid, int64_t ldr,
+                        const float* gate, void* stream);
+
 /* Same kernel under the two names a binding would look for. */
 int dax_gemm_i8_dequant(const void* qx, const float* sx, const void* qw, const float* sw, const void* bias,
                         int bias_dtype, void* out, int out_dtype, int64_t M, int64_t N, int64_t K,
@@ -165,6 +176,21 @@ int dax_rmsnorm_rope_pack(const void* x, int dtype, int64_t s, int64_t D, int64_
                           int64_t n_partials, int do_norm, const void* norm_weight, float eps,
                           const float* rope_cos, const float* rope_sin, int64_t token_offset, void* out,
                           int64_t ldo, int64_t col_group, int64_t group_stride, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * LayerNorm + adaLN modulation (+ per-token quantisation): the step in front of every quantised linear
+ * of a Wan DiT block outside the attention itself (the block is diffusers code called from
+ * dax/adapters/wan/transformer_adapter.py:130-136; the quantiser it absorbs is
+ * dax/quant/nn/dynamic/functional.py:54-148).
+ *   y = round_dtype( LN(x; eps) [* ln_weight + ln_bias] [* (1 + scale) + shift] )      per token row
+ *   (q, qscale) = per-token dynamic quantisation of y (bit-exact with dax_quant_rowwise applied to y)
+ * x [s, D] (ldx) BF16/F16; ln_weight, ln_bias, shift, scale: [D] fp32 or NULL; y [s, D] (ldy) or NULL;
+ * q [s, D] of q_dtype + qscale [s] or NULL (at least one output).  D % 8 == 0, D <= 8192.
+ * ------------------------------------------------------------------------------------------- */
+int dax_layernorm_modulate_quant(const void* x, int dtype, int64_t s, int64_t D, int64_t ldx,
+                                 const float* ln_weight, const float* ln_bias, const float* shift,
+                                 const float* scale, float eps, void* y, int64_t ldy, void* q, int q_dtype,
+                                 float* qscale, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Quantised non-causal attention (replaces the attention dispatch at

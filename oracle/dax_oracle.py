@@ -324,3 +324,54 @@ def rel_l2(a: torch.Tensor, b: torch.Tensor) -> float:
 def cosine(a: torch.Tensor, b: torch.Tensor) -> float:
     a, b = a.double().flatten(), b.double().flatten()
     return float((a @ b) / (a.norm() * b.norm()).clamp_min(1e-300))
+
+
+# ----------------------------------------------------------------------------------------------
+# the rest of a Wan DiT block and the DiT step around the hot path (published architecture; the block
+# itself is diffusers code called from dax/adapters/wan/transformer_adapter.py:130-136: parity unpinned)
+# ----------------------------------------------------------------------------------------------
+def layernorm(x: torch.Tensor, weight=None, bias=None, eps: float = 1e-6) -> torch.Tensor:
+    """LayerNorm over the last dimension evaluated in fp32, result fp32."""
+    xf = x.float()
+    return F.layer_norm(xf, xf.shape[-1:], None if weight is None else weight.float(),
+                        None if bias is None else bias.float(), eps)
+
+
+class QuantLinear:
+    """A float linear after the module swap: per-channel quantised weight + dynamic per-token activations."""
+
+    def __init__(self, w: torch.Tensor, b: Optional[torch.Tensor], weight_dtype=torch.int8, act_dtype=torch.int8):
+        self.qw, self.sw = quantize_weight(w, weight_dtype)
+        self.b, self.weight_dtype, self.act_dtype = b, weight_dtype, act_dtype
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        if self.weight_dtype == torch.int8:
+            return linear_int8(x, self.qw, self.sw, self.b, x.dtype)
+        return linear_fp8(x, self.qw, self.sw, self.b, x.dtype, self.act_dtype)
+
+
+def attention_block(x, ctx, lins, norm_q_w, norm_k_w, heads, freqs, eps=1e-6):
+    """Self- (ctx None) or cross-attention with Q/K RMSNorm, optional RoPE, fp32 SDPA, O projection
+    (``dax/adapters/wan/attn_adapter.py:62-304``); ``lins`` = (q, k, v, o) callables."""
+    kv = x if ctx is None else ctx
+    q = rmsnorm(lins[0](x), norm_q_w, eps).unflatten(2, (heads, -1)).transpose(1, 2)
+    k = rmsnorm(lins[1](kv), norm_k_w, eps).unflatten(2, (heads, -1)).transpose(1, 2)
+    v = lins[2](kv).unflatten(2, (heads, -1)).transpose(1, 2)
+    if freqs is not None:
+        q, k = apply_rotary_emb(q, freqs), apply_rotary_emb(k, freqs)
+    o = sdpa_fp32(q, k, v).to(x.dtype).transpose(1, 2).flatten(2, 3)
+    return lins[3](o)
+
+
+def wan_block(h, ctx, temb6, table6, attn1, attn2, norm2_w, norm2_b, ffn_up, ffn_down, heads, freqs, eps=1e-6):
+    """One Wan2.1 block.  ``temb6 [B,6,D]`` + ``table6 [1,6,D]`` give shift/scale/gate of the self-attention
+    and of the FFN; ``attn1`` / ``attn2`` = (q, k, v, o, norm_q_w, norm_k_w)."""
+    shift_msa, scale_msa, gate_msa, c_shift, c_scale, c_gate = (table6.float() + temb6.float()).chunk(6, dim=1)
+    n = (layernorm(h, eps=eps) * (1 + scale_msa) + shift_msa).type_as(h)
+    a = attention_block(n, None, attn1[:4], attn1[4], attn1[5], heads, freqs, eps)
+    h = (h.float() + a * gate_msa).type_as(h)
+    n = layernorm(h, norm2_w, norm2_b, eps).type_as(h)
+    h = h + attention_block(n, ctx, attn2[:4], attn2[4], attn2[5], heads, None, eps)
+    n = (layernorm(h, eps=eps) * (1 + c_scale) + c_shift).type_as(h)
+    f = ffn_down(F.gelu(ffn_up(n), approximate="tanh"))
+    return (h.float() + f.float() * c_gate).type_as(h)

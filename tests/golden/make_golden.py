@@ -14,6 +14,7 @@ The reference has no tests or fixtures of its own, so these files pin the oracle
   microbatch.pt   dax.parallel.patches.wanx2_1_t2v_opt.micro_batch_project_O_strategy
   layout.pt       the reshape/permute pairs around all_to_all_single in
                   dax.parallel.patches.wanx2_1_t2v_opt.layer (exchange emulated in-process)
+  teacache.pt     dax.cache.teacache: skip decisions and accumulators over a synthetic schedule
 Tensors are small (a few hundred KB in total).
 """
 import os
@@ -127,6 +128,41 @@ def main():
         pre2.append(pre_all2all_fun(pi, ish, got[r]))
     back = [post_all2all(po2, rsh2)(o) for o in exchange(pre2)]        # [1, s, H, d] per rank
     torch.save({"shards": shards, "tokens": got, "heads": back}, os.path.join(HERE, "layout.pt"))
+
+    # ---- TeaCache: skip decisions over a synthetic 20-step CFG schedule (40 calls) ----
+    import dax.cache.teacache as ref_tc
+
+    class Dummy:
+        enable_teacache = True
+        cnt = 0
+        teacache_thresh = 0.2
+        use_ref_steps = True
+        coefficients = [-3.03318725e05, 4.90537029e04, -2.65530556e03, 5.87365115e01, -3.15583525e-01]
+        ret_steps = 5 * 2
+        cutoff_steps = 20 * 2
+        accumulated_rel_l1_distance_even = 0
+        accumulated_rel_l1_distance_odd = 0
+        previous_e0_even = None
+        previous_e0_odd = None
+        previous_residual_even = None
+        previous_residual_odd = None
+
+    d = Dummy()
+    base = torch.randn(1, 6, 64, generator=g)
+    drift = torch.randn(1, 6, 64, generator=g)
+    inputs, skips, accs = [], [], []
+    for step in range(20):
+        for branch in range(2):
+            tp = base + drift * (0.02 * step + 0.005 * branch) * (1.0 + 0.3 * torch.sin(torch.tensor(float(step))))
+            inputs.append(tp)
+            skips.append(bool(ref_tc.should_skip_forward_for_cached_states(d, timestep_proj=tp, temb=tp[:, 0])))
+            accs.append((float(d.accumulated_rel_l1_distance_even), float(d.accumulated_rel_l1_distance_odd)))
+    hs, orig = torch.randn(1, 5, 8, generator=g), torch.randn(5, 8, generator=g)
+    d.is_even = True
+    ref_tc.maybe_cache_states(d, hs, orig)
+    torch.save({"inputs": inputs, "skips": skips, "accs": accs, "hs": hs, "orig": orig,
+                "residual": d.previous_residual_even, "retrieved": ref_tc.retrieve_cached_states(d, orig)},
+               os.path.join(HERE, "teacache.pt"))
     print("golden vectors written to", HERE)
 
 
