@@ -1,7 +1,11 @@
 #!/usr/bin/env python
-"""Benchmark of the DiT-step hot path: the self-attention blocks of one Wan2.1-14B-shaped denoising
-step at 720p / 81 frames (40 layers, 75,600 tokens on a 21x45x80 grid, hidden 5120, 40 heads of 128,
+"""Benchmark of one Wan2.1-14B-shaped DiT denoising step at 720p / 81 frames (latents 16x21x90x160 ->
+75,600 tokens on a 21x45x80 grid; 40 blocks, hidden 5120, 40 heads of 128, FFN 13,824, 512 text tokens;
 FP8-e4m3 dynamic linears, INT8-QK / FP8-PV attention), Ulysses sequence parallel over N GPUs.
+
+    --workload dit       (default) the whole DiT forward: patch embedding, condition embedder, 40 x
+                         (self-attention block, cross-attention, FFN), output head
+    --workload hotpath   only the 40 self-attention blocks (the hot path proper)
 
     python bench.py [--gpus N] [--steps K] [--warmup W]            (N > 1: launched by torchrun)
     python bench.py --impl reference ...                            CPU arm: the reference's algorithm
@@ -31,12 +35,17 @@ import torch  # noqa: E402
 GRID = (21, 45, 80)
 TOKENS = GRID[0] * GRID[1] * GRID[2]  # 75,600
 DIM, HEADS, HEAD_DIM, LAYERS = 5120, 40, 128, 40
-METRIC = "wan2.1-14b_dit_step_self_attention_hot_path_ms_720p"
+FFN, TEXT_TOKENS, TEXT_DIM = 13824, 512, 4096
+LATENT = (1, 16, 21, 90, 160)
+METRICS = {"dit": "wan2.1-14b_dit_step_ms_720p", "hotpath": "wan2.1-14b_dit_step_self_attention_hot_path_ms_720p"}
 
 
-def flops_per_step(tokens: int = TOKENS) -> float:
+def flops_per_step(tokens: int = TOKENS, workload: str = "hotpath") -> float:
     attn = 4.0 * HEADS * tokens * tokens * HEAD_DIM
     lin = 4 * 2.0 * tokens * DIM * DIM
+    if workload == "dit":  # + cross-attention (q, o on tokens; k, v on the text; attention) + FFN
+        lin += 2 * 2.0 * tokens * DIM * DIM + 2 * 2.0 * TEXT_TOKENS * DIM * DIM + 2 * 2.0 * tokens * DIM * FFN
+        attn += 4.0 * HEADS * tokens * TEXT_TOKENS * HEAD_DIM
     return LAYERS * (attn + lin)
 
 
@@ -81,7 +90,7 @@ class ClockSampler:
 # ----------------------------------------------------------------------------------------------
 # CPU arm: the reference's algorithm (oracle port) on the host cores, bounded sample
 # ----------------------------------------------------------------------------------------------
-def cpu_hot_path_ms(sample_rows: int = 2048, sample_queries: int = 1024, repeats: int = 2):
+def cpu_hot_path_ms(sample_rows: int = 2048, sample_queries: int = 1024, repeats: int = 2, workload: str = "hotpath"):
     """Time the reference's CPU-runnable path (its dynamic quantised linear + fp32 SDPA,
     dax/quant/nn/dynamic/linear.py:145-228 and dax/adapters/wan/attn_adapter.py:222-229, as restated in
     oracle/) on a bounded sample and scale it to one full step.  Linears are timed on `sample_rows` of
@@ -104,9 +113,13 @@ def cpu_hot_path_ms(sample_rows: int = 2048, sample_queries: int = 1024, repeats
     for _ in range(repeats):
         O.sdpa_fp32(q, k, v)
     t_att = (time.perf_counter() - t0) / repeats * (TOKENS / sample_queries) * HEADS
-    step_ms = LAYERS * (4 * t_lin + t_att) * 1e3
-    sample = (f"1 layer: FP8 linear on {sample_rows} of {TOKENS} rows x4, fp32 SDPA on {sample_queries} query rows of 1 head "
-              f"x all keys; scaled linearly to {LAYERS} layers, {TOKENS} rows, {HEADS} heads")
+    lin_units = 4.0  # in units of one 5120 -> 5120 linear over all tokens
+    if workload == "dit":  # cross-attention q/o, FFN up/down (cost proportional to K x N); text-side terms negligible
+        lin_units += 2.0 + 2.0 * FFN / DIM
+        t_att *= 1.0 + TEXT_TOKENS / TOKENS
+    step_ms = LAYERS * (lin_units * t_lin + t_att) * 1e3
+    sample = (f"1 layer: FP8 linear 5120->5120 on {sample_rows} of {TOKENS} rows (x{lin_units:.1f} by K x N), fp32 SDPA on "
+              f"{sample_queries} query rows of 1 head x all keys; scaled linearly to {LAYERS} layers, {TOKENS} rows, {HEADS} heads")
     return step_ms, threads, sample
 
 
@@ -119,21 +132,24 @@ def run_reference_arm(args, rank: int):
         cpu_hot_path_ms(256, 64)
     threads = sample = None
     for _ in range(min(steps, 3)):
-        ms, threads, sample = cpu_hot_path_ms()
+        ms, threads, sample = cpu_hot_path_ms(workload=args.workload)
         vals.append(ms)
     ms = statistics.mean(vals)
-    line = {"impl": "reference", "metric": METRIC, "value": ms, "unit": "ms", "n_gpus": args.gpus, "steps": args.steps,
+    line = {"impl": "reference", "metric": METRICS[args.workload], "value": ms, "unit": "ms", "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
             "dtype": "fp32 SDPA + fp8 linears (CPU)", "data": "synthetic",
-            "config": workload_config(args.gpus),
+            "config": workload_config(args.gpus, args.workload),
             "cpu_baseline": {"value": ms, "unit": "ms", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": ms, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
 
-def workload_config(n: int):
-    return {"workload": "cfg5 hot path: 40 self-attention blocks of a Wan2.1-14B-shaped DiT step, 720p/81 frames, "
+def workload_config(n: int, workload: str = "hotpath"):
+    what = ("one full DiT forward (patch embedding, condition embedder, 40 x [self-attention, cross-attention over 512 text "
+            "tokens, FFN 13,824], output head) of a Wan2.1-14B-shaped model" if workload == "dit"
+            else "hot path only: the 40 self-attention blocks of a Wan2.1-14B-shaped DiT step")
+    return {"workload": f"cfg5 step: {what}, 720p/81 frames, "
                         "75,600 tokens (21x45x80), dim 5120, 40 heads x 128, FP8-e4m3 dynamic linears, "
                         "INT8-QK/FP8-PV attention, RMSNorm + 3-D RoPE",
             "tokens": TOKENS, "layers": LAYERS, "parallelism": f"ulysses_sp{n}", "overlap_comm": n > 1,
@@ -149,6 +165,7 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="dax_b200", choices=["dax_b200", "reference"])
+    ap.add_argument("--workload", default="dit", choices=["dit", "hotpath"])
     ap.add_argument("--layers", type=int, default=LAYERS, help=argparse.SUPPRESS)  # profiling captures only
     ap.add_argument("--tokens", type=int, default=TOKENS, help=argparse.SUPPRESS)  # profiling captures only
     ap.add_argument("--no-cpu-baseline", action="store_true", help=argparse.SUPPRESS)
@@ -180,30 +197,44 @@ def main():
     assert tokens % world == 0 and HEADS % world == 0
     s = tokens // world
 
-    # ---- model: random-init weights N(0, 0.02), zero bias, built layer by layer on the device ----
+    # ---- model: random-init weights N(0, 0.02), zero bias, created directly on the device ----
+    from dax_b200.adapters.wan.modules import WanDiT
     torch.manual_seed(1234)
+    dit = args.workload == "dit"
     with torch.device("meta"):
-        stack = WanSelfAttentionStack(layers, DIM, HEADS)
-    stack = stack.to_empty(device=dev).to(torch.bfloat16)
-    g = torch.Generator(device=dev).manual_seed(1234)
+        model = (WanDiT(layers=layers, dim=DIM, ffn_dim=FFN, heads=HEADS, text_dim=TEXT_DIM) if dit
+                 else WanSelfAttentionStack(layers, DIM, HEADS))
+    model = model.to_empty(device=dev).to(torch.bfloat16)
+    g = torch.Generator(device=dev).manual_seed(1234)  # same stream on every rank: identical replicas
     with torch.no_grad():
-        for p_name, p in stack.named_parameters():
-            if p_name.endswith("norm_q.weight") or p_name.endswith("norm_k.weight"):
+        for p_name, p in model.named_parameters():
+            if p_name.endswith(("norm_q.weight", "norm_k.weight", "norm2.weight")):
                 p.fill_(1.0)
             elif p_name.endswith("bias"):
                 p.zero_()
+            elif "scale_shift_table" in p_name:
+                p.copy_((torch.randn(p.shape, generator=g, device=dev) / DIM ** 0.5).to(p.dtype))
             else:
                 p.copy_((torch.randn(p.shape, generator=g, device=dev) * 0.02).to(p.dtype))
-    pipe = _Pipe(stack)
+    pipe = _Pipe(model)
     optimize_pipe(pipe, sequence_parallel=sp, compile=False, overlap_comm=sp, fp8_linear=True,
                   attention_mode=args.attention_mode)
     torch.cuda.empty_cache()
-    rope = wan_rope_table(GRID if tokens == TOKENS else (1, 1, tokens), device=dev)
 
     gx = torch.Generator().manual_seed(99)
-    x_full = torch.randn(1, tokens, DIM, generator=gx).to(torch.bfloat16)
-    x_host = x_full[:, rank * s:(rank + 1) * s].contiguous().pin_memory()
-    y_host = torch.empty_like(x_host).pin_memory()
+    if dit:
+        assert tokens == TOKENS, "--tokens applies to --workload hotpath only"
+        x_host = torch.randn(LATENT, generator=gx).to(torch.bfloat16).pin_memory()  # replicated latent, split inside
+        text = torch.randn(1, TEXT_TOKENS, TEXT_DIM, generator=gx).to(torch.bfloat16).to(dev)
+        timestep = torch.randint(0, 1000, (1,), generator=gx).to(dev)
+        y_host = torch.empty(LATENT, dtype=torch.bfloat16).pin_memory()
+        h2d_bytes = d2h_bytes = x_host.numel() * 2 * world
+    else:
+        rope = wan_rope_table(GRID if tokens == TOKENS else (1, 1, tokens), device=dev)
+        x_full = torch.randn(1, tokens, DIM, generator=gx).to(torch.bfloat16)
+        x_host = x_full[:, rank * s:(rank + 1) * s].contiguous().pin_memory()
+        y_host = torch.empty_like(x_host).pin_memory()
+        h2d_bytes = d2h_bytes = x_host.numel() * 2 * world
     x_dev = x_host.to(dev)
 
     def barrier():
@@ -213,6 +244,8 @@ def main():
 
     def step(x):
         with torch.no_grad():
+            if dit:
+                return pipe.transformer(x, timestep, text, return_dict=False)[0]
             return pipe.transformer(x, rotary_emb=rope)
 
     for _ in range(args.warmup):
@@ -279,24 +312,28 @@ def main():
     calls, att_ms, metas = trace.get("attn_forward", (0, 0.0, []))
     att_flops = sum(4.0 * m[0] * m[1] * m[2] * m[3] * HEAD_DIM for m in metas)
     achieved = att_flops / (att_ms * 1e-3) / 1e12 if att_ms > 0 else None
+    # DRAM traffic per launch: ncu measured 392 MB for a 40-head, 16,384-token launch (profiles/), 0.936 of the
+    # compulsory operand bytes (INT8 Q 128 B + bf16 O 256 B per query row, INT8 K + FP8 V 256 B per key row, per head);
+    # it grows in proportion to rows x heads, so the same factor is applied to the launches timed here
+    traffic = (sum(0.936 * m[0] * m[1] * (384.0 * m[2] + 256.0 * m[3]) for m in metas) / calls) if calls else None
     roofline = {"bound": "tensor", "kernel": "attn_fwd_kernel", "achieved": achieved, "peak": peak8, "unit": "TFLOP/s",
-                "frac": achieved / peak8 if achieved else None, "traffic": None, "peak_source": peak_src,
+                "frac": achieved / peak8 if achieved else None, "traffic": traffic, "peak_source": peak_src,
                 "launches": calls, "avg_launch_ms": att_ms / calls if calls else None,
                 "share_of_step": att_ms / (ms_step * args.steps) if calls else None}
     breakdown = {k: {"calls": c, "ms_per_step": tms / args.steps} for k, (c, tms, _) in trace.items()}
 
     cpu = None
     if not args.no_cpu_baseline:
-        ms, threads, sample = cpu_hot_path_ms()
+        ms, threads, sample = cpu_hot_path_ms(workload=args.workload)
         cpu = {"value": ms, "unit": "ms", "cores": threads, "kind": "port", "sample": sample}
 
-    line = {"metric": METRIC, "value": ms_step, "unit": "ms", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+    line = {"metric": METRICS[args.workload], "value": ms_step, "unit": "ms", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
             "dtype": "int8/fp8 (fp32 accumulate)", "data": "synthetic",
-            "config": workload_config(world) if full else {"workload": f"REDUCED profiling case: {layers} layers, {tokens} tokens"},
-            "tflops": flops_per_step(tokens) * layers / LAYERS / (ms_step * 1e-3) / 1e12,
-            "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": x_host.numel() * 2 * world,
-                    "d2h_bytes_per_step": y_host.numel() * 2 * world},
+            "config": workload_config(world, args.workload) if full else
+            {"workload": f"REDUCED profiling case ({args.workload}): {layers} layers, {tokens} tokens"},
+            "tflops": flops_per_step(tokens, args.workload) * layers / LAYERS / (ms_step * 1e-3) / 1e12,
+            "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
             "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
             "kernel_ms_per_step": breakdown}
     print(json.dumps(line), flush=True)
