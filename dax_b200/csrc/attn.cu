@@ -11,8 +11,8 @@
 //                 (warps w and w+4 share the rows of TMEM lane quarter w%4 and split the columns)
 //   warps 8..15   the same for tile 1
 //   warp  16      TMA producer: both Q tiles once, then K_0, V_0, K_1, V_1, ... through a ring
-//   warp  17      MMA issuer for Q.K^T of both tiles (one thread)
-//   warps 18, 19  MMA issuers for P.V of tile 0 / tile 1 (one thread each)
+//   warps 17..    MMA issuers, one thread each: two (one per tile: Q.K^T of the next KV tile, then P.V of this
+//                 one) or three (Q.K^T of both tiles; P.V of tile 0; P.V of tile 1), see AttnCfg
 // Four softmax warps per scheduler instead of two: the softmax is a chain of dependent fixed-latency
 // operations around a 16-per-clock exp unit, and only more resident warps hide that latency.  The two
 // threads of a row agree on the row maximum through a sequence-stamped shared-memory slot (no CTA or
@@ -39,16 +39,30 @@ namespace {
 #ifdef DAX_ATTN_PROFILE
 // Phase timing for kernel tuning: compiled only when the macro is given on the command line.
 __device__ unsigned long long g_attn_prof[16];
-#define PROF_DECL unsigned long long prof_t0 = clock64(), prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define PROF_DECL unsigned long long prof_t0 = clock64(), prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0}
 #define PROF_MARK(i) do { unsigned long long t_ = clock64(); prof_acc[i] += t_ - prof_t0; prof_t0 = t_; } while (0)
-#define PROF_FLUSH() do { if (blockIdx.x == 3 && blockIdx.y == 0 && warp == 5 && lane == 0) { for (int i_ = 0; i_ < 8; ++i_) g_attn_prof[i_] = prof_acc[i_]; g_attn_prof[8] = n_kv; } } while (0)
+#define PROF_FLUSH() do { if (blockIdx.x == 3 && blockIdx.y == 0 && warp == DAX_ATTN_PROFILE && lane == 0) { for (int i_ = 0; i_ < 10; ++i_) g_attn_prof[i_] = prof_acc[i_]; g_attn_prof[15] = n_kv; } } while (0)
 #else
 #define PROF_DECL
 #define PROF_MARK(i)
 #define PROF_FLUSH()
 #endif
 
-constexpr int ATT_THREADS = 640;
+#ifdef DAX_ATTN_TRACE
+// Event timestamps of one CTA for a few KV iterations (kernel tuning only).
+__device__ unsigned long long g_attn_trace[20 * 8 * 12];
+#define TR(ev) do { if (blockIdx.x == 3 && blockIdx.y == 0 && lane == 0 && j >= 60 && j < 68) g_attn_trace[(warp * 8 + (j - 60)) * 12 + (ev)] = clock64(); } while (0)
+#else
+#define TR(ev)
+#endif
+
+constexpr int PRODUCER_WARP = 16;
+#ifndef DAX_ATTN_ISSUERS_8BIT
+#define DAX_ATTN_ISSUERS_8BIT 2
+#endif
+#ifndef DAX_ATTN_ISSUERS_16BIT
+#define DAX_ATTN_ISSUERS_16BIT 3
+#endif
 constexpr int SOFTMAX_WARPS = 16;
 constexpr int BOX_BYTES = 128 * 128;  // one [128 x 128 B] box
 
@@ -56,7 +70,8 @@ template <int MODE> struct AttnCfg;
 template <> struct AttnCfg<DAX_ATTN_QK_I8_PV_F8> {
   static constexpr int QK_KIND = KIND_I8, PV_KIND = KIND_F8;
   static constexpr int EQ = 1, EP = 1;       // bytes per element of Q/K and of P/V
-  static constexpr int NSLOT = 8;
+  static constexpr int NSLOT = 8;            // 8 x 16 KB: four (K, V) pairs in flight
+  static constexpr int ISSUERS = DAX_ATTN_ISSUERS_8BIT;
   static constexpr float TAU = 0.f;          // P is scaled to the e4m3 range: the row max must be exact
   static constexpr float PBIAS = 8.8073549f; // log2(448): P in (0, 448]
 };
@@ -64,6 +79,7 @@ template <> struct AttnCfg<DAX_ATTN_QK_BF16_PV_BF16> {
   static constexpr int QK_KIND = KIND_F16, PV_KIND = KIND_F16;
   static constexpr int EQ = 2, EP = 2;
   static constexpr int NSLOT = 2;            // 2 x 32 KB: shared memory is full (Q 64 KB + P 64 KB + ring 64 KB)
+  static constexpr int ISSUERS = DAX_ATTN_ISSUERS_16BIT;
   static constexpr float TAU = 8.f;          // lazy rescale: P <= 2^8, far inside the bf16 range
   static constexpr float PBIAS = 0.f;
 };
@@ -71,9 +87,19 @@ template <> struct AttnCfg<DAX_ATTN_QK_I8_PV_BF16> {
   static constexpr int QK_KIND = KIND_I8, PV_KIND = KIND_F16;
   static constexpr int EQ = 1, EP = 2;
   static constexpr int NSLOT = 3;            // 3 x 32 KB (K tiles use half a slot): Q 32 KB + P 64 KB + ring 96 KB
+  static constexpr int ISSUERS = DAX_ATTN_ISSUERS_16BIT;
   static constexpr float TAU = 8.f;
   static constexpr float PBIAS = 0.f;
 };
+
+// 16 softmax warps, the producer warp, the issuer warps: at most 20 warps, i.e. five per scheduler, which
+// is what leaves 96 registers per thread
+template <int MODE>
+constexpr int att_threads() { return 32 * (SOFTMAX_WARPS + 1 + AttnCfg<MODE>::ISSUERS); }
+// The kernel is always compiled for the register budget of 640 threads (96 per thread, which is also what it
+// uses).  With the bound at 608 threads the compiler still uses 96 registers but schedules the softmax loop
+// differently, and the INT8/FP8 kernel ran 15 % slower.
+constexpr int ATT_BOUND_THREADS = 640;
 
 template <int MODE>
 struct Smem {
@@ -84,7 +110,8 @@ struct Smem {
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_P = OFF_Q + 2 * Q_TILE;
   static constexpr int OFF_RING = OFF_P + 2 * P_TILE;
-  static constexpr int OFF_BAR = OFF_RING + C::NSLOT * SLOT;
+  static constexpr int OFF_BIAS = OFF_RING + C::NSLOT * SLOT;  // constant tile that seeds the score accumulators
+  static constexpr int OFF_BAR = OFF_BIAS + (C::QK_KIND == KIND_I8 ? BOX_BYTES : 0);
   static constexpr int OFF_VSCALE = OFF_BAR + 256;
   static constexpr int OFF_XCHG = OFF_VSCALE + 512;           // [2 tiles][2 parities][2 halves][128 rows] x 8 B
   static constexpr int TOTAL = OFF_XCHG + 2 * 2 * 2 * 128 * 8 + 1024 /*alignment slack*/;
@@ -147,52 +174,64 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
   return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
 }
 
-// Maximum of the scaled scores over the 64 columns a thread owns.  The scale is positive, so for
-// integer accumulators the maximum is taken on the integers and scaled once.
-template <int MODE, bool FULL>
-__device__ __forceinline__ float row_max64(const uint32_t (&sv)[64], float cmul, int valid) {
+// Integer score accumulators start from the bit pattern of 1.5 * 2^23 (see the MMA issuer), so that the
+// register a thread reads IS the float 12582912 + acc: no conversion instruction per element.
+constexpr float kAccBias = 12582912.f;
+
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// Columns >= valid of the last KV tile are padding: give them the score -inf, which is never the row maximum
+// and whose exponential is exactly zero whatever the (positive) scale; read as a biased integer accumulator
+// the same bit pattern behaves identically, because the scores only ever go through max and one FMA.
+// Only the last KV tile of a ragged sequence takes this path, so the hot loop carries one copy of the
+// max / exponential code and no per-column predicate.
+__device__ __forceinline__ void mask_padding64(uint32_t (&sv)[64], int valid) {
+#pragma unroll
+  for (int i = 0; i < 64; ++i) sv[i] = i < valid ? sv[i] : 0xFF800000u;
+}
+
+// Maximum of the scaled scores over the 64 columns a thread owns.  The scale is positive, so the maximum is
+// taken on the raw accumulators (two columns per instruction) and scaled once.
+template <int MODE>
+__device__ __forceinline__ float row_max64(const uint32_t (&sv)[64], float cmul) {
   using C = AttnCfg<MODE>;
-  if constexpr (C::QK_KIND == KIND_I8) {
-    int imax[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN};
+  float fmx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-    for (int i = 0; i < 64; ++i)
-      if (FULL || i < valid) imax[i & 3] = max(imax[i & 3], static_cast<int>(sv[i]));
-    return static_cast<float>(max(max(imax[0], imax[1]), max(imax[2], imax[3]))) * cmul;
-  } else {
-    float fmx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-    for (int i = 0; i < 64; ++i)
-      if (FULL || i < valid) fmx[i & 3] = fmaxf(fmx[i & 3], __uint_as_float(sv[i]));
-    return fmaxf(fmaxf(fmx[0], fmx[1]), fmaxf(fmx[2], fmx[3])) * cmul;
-  }
+  for (int i = 0; i < 64; i += 2)
+    fmx[(i >> 1) & 3] = fmax3(fmx[(i >> 1) & 3], __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+  const float mx = fmaxf(fmax3(fmx[0], fmx[1], fmx[2]), fmx[3]);
+  if constexpr (C::QK_KIND == KIND_I8) return (mx - kAccBias) * cmul;
+  else return mx * cmul;
 }
 
 // p_i = 2^(s_i * cmul + off) for the 64 columns held in sv (columns 64*half .. 64*half+63 of the tile);
 // converts to the P format, writes them into the K-major 128-byte-swizzled P tile and returns the
 // fp32 partial row sum (four independent partial sums keep the add chain short).
-template <int MODE, bool FULL>
-__device__ __forceinline__ float exp_and_store64(const uint32_t (&sv)[64], float cmul, float off, int valid,
-                                                 uint8_t* p_tile, int r, int half) {
+template <int MODE>
+__device__ __forceinline__ float exp_and_store64(const uint32_t (&sv)[64], float cmul, float off, uint8_t* p_tile,
+                                                 int r, int half) {
   using C = AttnCfg<MODE>;
-  // int -> float by the 1.5 * 2^23 bias trick (|acc| <= 127*127*128 < 2^22), folded into the FMA
-  const float off2 = fmaf(-12582912.f, cmul, off);
-  auto pv = [&](int i) -> float {
-    float v;
-    if constexpr (C::QK_KIND == KIND_I8) v = ex2(fmaf(__uint_as_float(sv[i] + 0x4B400000u), cmul, off2));
-    else v = ex2(fmaf(__uint_as_float(sv[i]), cmul, off));
-    return (FULL || i < valid) ? v : 0.f;
-  };
+  // integer accumulators arrive as 12582912 + acc (|acc| <= 127*127*128 < 2^22): the bias folds into the FMA
+  const float off2 = C::QK_KIND == KIND_I8 ? fmaf(-kAccBias, cmul, off) : off;
   float sum[4] = {0.f, 0.f, 0.f, 0.f};
+  auto pv = [&](int i) -> float {
+    const float e = ex2(fmaf(__uint_as_float(sv[i]), cmul, off2));
+    sum[i & 3] += e;
+    return e;
+  };
   if constexpr (C::EP == 1) {
     // one row of the P tile is 128 bytes: this thread owns 16-byte chunks 4*half .. 4*half+3
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
+      // sixteen exponentials per 16-byte store: converting and storing in these batches interleaves the
+      // conversions with the next batch's exponentials (all 64 at once was 15 % slower)
       float e[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        e[i] = pv(16 * c + i);
-        sum[i & 3] += e[i];
-      }
+      for (int i = 0; i < 16; ++i) e[i] = pv(16 * c + i);
       uint4 w;
 #ifdef DAX_ATTN_X_NOCVT  // tuning experiment only (wrong results): no FP8 conversion
       w.x = __float_as_uint(e[0] + e[1] + e[2] + e[3]);
@@ -214,10 +253,7 @@ __device__ __forceinline__ float exp_and_store64(const uint32_t (&sv)[64], float
     for (int c = 0; c < 8; ++c) {
       float e[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        e[i] = pv(8 * c + i);
-        sum[i & 3] += e[i];
-      }
+      for (int i = 0; i < 8; ++i) e[i] = pv(8 * c + i);
       uint4 w;
       w.x = pack_bf16x2_trunc(e[0], e[1]);
       w.y = pack_bf16x2_trunc(e[2], e[3]);
@@ -250,7 +286,7 @@ __device__ __forceinline__ bool xchg_read(const uint2* slot, uint32_t seq, float
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(ATT_THREADS, 1)
+__global__ void __launch_bounds__(ATT_BOUND_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
   using C = AttnCfg<MODE>;
@@ -286,15 +322,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 256);
-      mbar_init(&s_free[i], 8);   // one arrival per softmax warp of the tile
+      mbar_init(&p_full[i], 8);   // one arrival per softmax warp of the tile
+      mbar_init(&s_free[i], 8);   // likewise
       mbar_init(&pv_done[i], 1);
     }
     *abort_flag = 0;
     mbar_fence_init();
   }
   if (threadIdx.x < 128) vscale_s[threadIdx.x] = p.v_scale[static_cast<int64_t>(bh) * 128 + threadIdx.x];
-  for (int i = threadIdx.x; i < 2 * 2 * 2 * 128; i += ATT_THREADS) xchg[i] = make_uint2(0u, 0u);
+  for (int i = threadIdx.x; i < 2 * 2 * 2 * 128; i += blockDim.x) xchg[i] = make_uint2(0u, 0u);
+  if constexpr (C::QK_KIND == KIND_I8) {
+    // [128 rows x 128 B] box, bf16, 128-byte swizzle: K elements 0..2 of every row are 2048, the rest 0, so that
+    // tile . tile^T = 3 * 2048^2 = 12582912 = 1.5 * 2^23 in every accumulator (logical chunk 0 of row r sits in
+    // physical chunk r & 7)
+    uint4* bias = reinterpret_cast<uint4*>(smem + L::OFF_BIAS);
+    for (int i = threadIdx.x; i < BOX_BYTES / 16; i += blockDim.x) {
+      const int r = i >> 3, ck = i & 7;
+      bias[i] = ck == (r & 7) ? make_uint4(0x45004500u, 0x00004500u, 0u, 0u) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    fence_proxy_async_smem();
+  }
   if (warp == SOFTMAX_WARPS) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
@@ -304,7 +351,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == SOFTMAX_WARPS) {
+  if (warp == PRODUCER_WARP) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&map_q);
@@ -321,6 +368,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         {  // K_j : [128 tokens x 128 channels]
           const uint32_t s = seq % C::NSLOT, ph = (seq / C::NSLOT) & 1u;
           if (!mbar_wait(&kv_empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+          TR(0);
           mbar_arrive_expect_tx(&kv_full[s], BOX_BYTES * C::EQ);
           for (int sub = 0; sub < C::EQ; ++sub)
             tma_load_2d(smem + L::OFF_RING + s * L::SLOT + sub * BOX_BYTES, &map_k, &kv_full[s], sub * 64,
@@ -330,6 +378,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         {  // V_j^T : [128 channels x 128 tokens]
           const uint32_t s = seq % C::NSLOT, ph = (seq / C::NSLOT) & 1u;
           if (!mbar_wait(&kv_empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+          TR(1);
           mbar_arrive_expect_tx(&kv_full[s], BOX_BYTES * C::EP);
           for (int sub = 0; sub < C::EP; ++sub)
             tma_load_2d(smem + L::OFF_RING + s * L::SLOT + sub * BOX_BYTES, &map_v, &kv_full[s],
@@ -338,46 +387,66 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
       }
     }
-  } else if (warp == SOFTMAX_WARPS + 1) {
-    // ---------------------------------------------------------------- MMA issuer: Q.K^T of both tiles
-    // Three issuer threads (this one and one per tile for P.V) so that a late softmax of one tile does
-    // not hold back work that is ready for the other: each thread only waits for its own inputs.
+  } else if (warp > SOFTMAX_WARPS && warp <= SOFTMAX_WARPS + C::ISSUERS) {
+    // ---------------------------------------------------------------- MMA issuers (one thread each)
+    // One thread cannot issue faster than one tcgen05.mma per ~100 clocks whatever the shape, while the pipe
+    // retires a 128x128x32 step in 64; two or more threads together reach the pipe's rate.
+    // Two issuers (8-bit Q.K^T): one per query tile, so that a tile never waits behind the other tile's
+    // barriers.  For its tile the events come in a fixed order: S(j) copied to registers -> Q.K^T(j+1) may
+    // overwrite it; then P(j) written -> P.V(j); then S(j+1) copied, and so on.
+    // Three issuers (16-bit Q.K^T, eight steps per product, the tensor pipe is the busiest unit): one for
+    // Q.K^T of both tiles, one per tile for P.V.
     if (lane == 0) {
-      // s8 x s8 -> s32, or bf16 x bf16 -> f32
+      const int role = warp - (SOFTMAX_WARPS + 1);
+      // s8 x s8 -> s32, or bf16 x bf16 -> f32;  e4m3 x e4m3 -> f32, or bf16 x bf16 -> f32
       constexpr uint32_t idesc_qk = C::QK_KIND == KIND_I8 ? make_idesc(2, 1, 1, 128, 128) : make_idesc(1, 1, 1, 128, 128);
-      const uint32_t q_addr = smem_u32(smem + L::OFF_Q);
-      const uint32_t ring = smem_u32(smem + L::OFF_RING);
-      bool ok = mbar_wait(q_full, 0, abort_flag);
-      for (int j = 0; ok && j < n_kv; ++j) {  // S_X(j) for both tiles
-        const uint32_t seq_k = 2 * j, slot = seq_k % C::NSLOT, ph = (seq_k / C::NSLOT) & 1u;
-        if (!mbar_wait(&kv_full[slot], ph, abort_flag)) { ok = false; break; }
-        for (int x = 0; x < 2; ++x) {
-          // S_X(j-1) has been copied to registers by all eight warps of the tile
-          if (j > 0 && !mbar_wait(&s_free[x], (j - 1) & 1u, abort_flag)) { ok = false; break; }
-          tc_fence_after_sync();
-          mma_tile<C::QK_KIND, C::EQ>(tmem_base + x * 128, q_addr + x * L::Q_TILE, ring + slot * L::SLOT, idesc_qk, false);
-          umma_commit(&s_full[x]);
-          umma_commit(&kv_empty[slot]);  // two arrivals free the slot: one per tile
-        }
-      }
-    }
-  } else if (warp >= SOFTMAX_WARPS + 2) {
-    // ---------------------------------------------------------------- MMA issuer: P.V of tile x
-    if (lane == 0) {
-      const int x = warp - (SOFTMAX_WARPS + 2);
-      // e4m3 x e4m3 -> f32, or bf16 x bf16 -> f32
       constexpr uint32_t idesc_pv = C::PV_KIND == KIND_F8 ? make_idesc(1, 0, 0, 128, 128) : make_idesc(1, 1, 1, 128, 128);
-      const uint32_t p_addr = smem_u32(smem + L::OFF_P) + x * L::P_TILE;
+      const uint32_t q_addr = smem_u32(smem + L::OFF_Q);
+      const uint32_t p_addr = smem_u32(smem + L::OFF_P);
       const uint32_t ring = smem_u32(smem + L::OFF_RING);
-      bool ok = true;
-      for (int j = 0; ok && j < n_kv; ++j) {
-        const uint32_t seq_v = 2 * j + 1, slot = seq_v % C::NSLOT, ph = (seq_v / C::NSLOT) & 1u;
-        if (!mbar_wait(&kv_full[slot], ph, abort_flag)) { ok = false; break; }
-        if (!mbar_wait(&p_full[x], j & 1u, abort_flag)) { ok = false; break; }
+      const uint64_t bias_desc = make_desc_k_sw128(smem_u32(smem + L::OFF_BIAS));
+      (void)bias_desc;
+      auto issue_qk = [&](int j, int x) -> bool {  // S_x(j) = Q_x . K_j^T
+        const uint32_t seq_k = 2 * j, slot = seq_k % C::NSLOT, ph = (seq_k / C::NSLOT) & 1u;
+        const uint32_t s_tm = tmem_base + x * 128;
+        if (!mbar_wait(&kv_full[slot], ph, abort_flag)) return false;
+        // S_x(j-1) has been copied to registers by all eight warps of the tile
+        if (j > 0 && !mbar_wait(&s_free[x], (j - 1) & 1u, abort_flag)) return false;
         tc_fence_after_sync();
-        mma_tile<C::PV_KIND, C::EP>(tmem_base + 256 + x * 128, p_addr, ring + slot * L::SLOT, idesc_pv, j > 0);
+        TR(0);
+        if constexpr (C::QK_KIND == KIND_I8) {
+          // one bf16 K=16 instruction writes the float 12582912 into every accumulator; the integer
+          // instructions then add the dot products to that bit pattern
+          umma_ss<KIND_F16>(s_tm, bias_desc, bias_desc, make_idesc(1, 1, 1, 128, 128), 0u);
+        }
+        mma_tile<C::QK_KIND, C::EQ>(s_tm, q_addr + x * L::Q_TILE, ring + slot * L::SLOT, idesc_qk, C::QK_KIND == KIND_I8);
+        umma_commit(&s_full[x]);
+        umma_commit(&kv_empty[slot]);  // two arrivals free the slot: one per tile
+        TR(2);
+        return true;
+      };
+      auto issue_pv = [&](int j, int x) -> bool {  // O_x += P_x . V_j
+        const uint32_t seq_v = 2 * j + 1, slot = seq_v % C::NSLOT, ph = (seq_v / C::NSLOT) & 1u;
+        if (!mbar_wait(&kv_full[slot], ph, abort_flag)) return false;
+        if (!mbar_wait(&p_full[x], j & 1u, abort_flag)) return false;
+        tc_fence_after_sync();
+        TR(1);
+        mma_tile<C::PV_KIND, C::EP>(tmem_base + 256 + x * 128, p_addr + x * L::P_TILE, ring + slot * L::SLOT, idesc_pv, j > 0);
         umma_commit(&pv_done[x]);
-        umma_commit(&kv_empty[slot]);  // the other tile's issuer supplies the second arrival
+        umma_commit(&kv_empty[slot]);  // the other tile's P.V supplies the second arrival
+        TR(3);
+        return true;
+      };
+      if constexpr (C::ISSUERS == 2) {
+        const int x = role;
+        bool ok = mbar_wait(q_full, 0, abort_flag) && issue_qk(0, x);
+        for (int j = 0; ok && j < n_kv; ++j) ok = (j + 1 >= n_kv || issue_qk(j + 1, x)) && issue_pv(j, x);
+      } else if (role == 0) {
+        bool ok = mbar_wait(q_full, 0, abort_flag);
+        for (int j = 0; ok && j < n_kv; ++j) ok = issue_qk(j, 0) && issue_qk(j, 1);
+      } else {
+        bool ok = true;
+        for (int j = 0; ok && j < n_kv; ++j) ok = issue_pv(j, role - 1);
       }
     }
   } else if (warp < SOFTMAX_WARPS) {
@@ -407,6 +476,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       if (!mbar_wait(&s_full[x], j & 1u, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
       PROF_MARK(0);
+      TR(0);
       uint32_t sv[64];
       tmem_ld32(s_tmem, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
       tmem_ld32(s_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
@@ -415,11 +485,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free[x]);  // S_X is in registers: Q.K^T of the next tile may start
       PROF_MARK(1);
+      TR(1);
 
       const float cmul = sq * kscale;
       const int valid = p.Sk - j * 128 - half * 64;  // columns >= valid are padding (only in the last tile)
-      const bool full = valid >= 64;
-      const float pm = full ? row_max64<MODE, true>(sv, cmul, valid) : row_max64<MODE, false>(sv, cmul, valid);
+      if (valid < 64) mask_padding64(sv, valid);
+      const float pm = row_max64<MODE>(sv, cmul);
+      TR(2);
 #ifdef DAX_ATTN_X_NOXCHG  // tuning experiment only (wrong results): no exchange with the partner thread
       float pm2 = pm;
 #else
@@ -428,6 +500,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       if (!xchg_read(slot(j & 1, half ^ 1), static_cast<uint32_t>(j + 1), pm2, abort_flag)) { ok = false; break; }
 #endif
       PROF_MARK(2);
+      TR(3);
       const float mx = fmaxf(pm, pm2);
       const float m_new = (mx > m + C::TAU) ? mx : m;
       const float alpha = ex2(m - m_new);  // m = -inf on the first tile -> 0
@@ -438,11 +511,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tc_fence_after_sync();
       }
       PROF_MARK(3);
-      const float sum = full ? exp_and_store64<MODE, true>(sv, cmul, off, valid, p_tile, r, half)
-                             : exp_and_store64<MODE, false>(sv, cmul, off, valid, p_tile, r, half);
+      TR(4);
+      PROF_MARK(8);
+      TR(5);
+      const float sum = exp_and_store64<MODE>(sv, cmul, off, p_tile, r, half);
       l = fmaf(l, alpha, sum);
       m = m_new;
       PROF_MARK(4);
+      TR(6);
 
       // correction: O_X *= alpha when any row of this warp moved its maximum (P_X . V_{j-1} is complete)
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
@@ -457,10 +533,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tmem_wait_st();
       }
       PROF_MARK(5);
+      TR(7);
       fence_proxy_async_smem();
       tc_fence_before_sync();
-      mbar_arrive(&p_full[x]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[x]);
       PROF_MARK(6);
+      TR(8);
     }
     PROF_FLUSH();
 
@@ -543,7 +622,8 @@ int launch_fwd(const AttnWorkspace& ws, const AttnParams& p, int64_t BH, cudaStr
   }
   DAX_CUDA(cudaFuncSetAttribute(attn_fwd_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
   dim3 grid(static_cast<unsigned>(p.n_ranges * p.tiles_per_range), static_cast<unsigned>(BH));
-  attn_fwd_kernel<MODE><<<grid, ATT_THREADS, L::TOTAL, st>>>(map_q, map_k, map_v, p);
+  static_assert(att_threads<MODE>() <= ATT_BOUND_THREADS, "more warps than the register budget allows");
+  attn_fwd_kernel<MODE><<<grid, att_threads<MODE>(), L::TOTAL, st>>>(map_q, map_k, map_v, p);
   DAX_CUDA(cudaGetLastError());
   return DAX_OK;
 }
@@ -594,6 +674,11 @@ extern "C" int dax_attn_forward(void* o, int dtype, int64_t B, int64_t heads, in
   return launch_fwd<DAX_ATTN_QK_BF16_PV_BF16>(ws, p, B * heads, st);
 }
 
+#ifdef DAX_ATTN_TRACE
+extern "C" int dax_attn_trace_read(unsigned long long* host, int n) {
+  return cudaMemcpyFromSymbol(host, dax::g_attn_trace, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : 4;
+}
+#endif
 #ifdef DAX_ATTN_PROFILE
 extern "C" int dax_attn_profile_read(unsigned long long* host16) {
   return cudaMemcpyFromSymbol(host16, dax::prof_symbol(), sizeof(unsigned long long) * 16) == cudaSuccess ? 0 : 4;
