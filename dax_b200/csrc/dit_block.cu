@@ -2,11 +2,13 @@
 // attention: the normalised, modulated activations feed a quantised linear, so the kernel can emit the
 // INT8 / FP8 codes and scales directly and the separate quantiser pass (and its HBM round trip) goes away.
 //
-// HBM-bound: 2 bytes read per element, 2 written (bf16 output) and/or 1 written (codes).  One CTA per
-// token row; the row lives in registers (128-bit loads); mean and centred variance are two CTA
-// reductions in fp32, the absmax of the rounded outputs a third.
+// HBM-bound: 2 bytes read per element, 2 written (bf16 output) and/or 1 written (codes).  CTAs stride over
+// the token rows; a row lives in registers (128-bit loads) and the next row's loads are already in flight;
+// mean and centred variance are two CTA reductions in fp32, the absmax of the rounded outputs a third.
 //   y = round_dtype( LN(x) [* w + b] [* (1 + scale) + shift] )          LN: eps inside the square root
 //   (q, s) = dynamic per-token quantisation of y, arithmetic of quant_common.cuh
+#include <algorithm>
+
 #include "quant_common.cuh"
 
 namespace dax {
@@ -26,10 +28,11 @@ template <bool BF16> __device__ __forceinline__ uint16_t from_f(float f) {
   else return __half_as_ushort(__float2half_rn(f));
 }
 
+// CTA-wide reductions through one of six shared buffers (three reductions per row, two rows' worth): a buffer
+// is rewritten two rows later, with three barriers in between, so one barrier per reduction is enough.
 __device__ __forceinline__ float block_sum(float v, float* red) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  __syncthreads();  // red may still be read from the previous reduction
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
   __syncthreads();
   float t = 0.f;
@@ -40,7 +43,6 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 __device__ __forceinline__ float block_max(float v, float* red) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  __syncthreads();
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
   __syncthreads();
   float t = red[0];
@@ -49,106 +51,121 @@ __device__ __forceinline__ float block_max(float v, float* red) {
   return t;
 }
 
-// QDT < 0: no quantised output
-template <bool BF16, int QDT>
+// QDT < 0: no quantised output.  NV = 16-byte vectors per thread (rows of up to NV * 2048 elements).
+template <bool BF16, int QDT, int NV>
 __global__ void __launch_bounds__(kThreads)
-ln_modulate_quant_kernel(const uint16_t* __restrict__ x, int64_t D, int64_t ldx, const float* __restrict__ w,
+ln_modulate_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D, int64_t ldx, const float* __restrict__ w,
                          const float* __restrict__ b, const float* __restrict__ shift,
                          const float* __restrict__ scale, float eps, uint16_t* __restrict__ y, int64_t ldy,
                          uint8_t* __restrict__ q, float* __restrict__ qscale) {
-  __shared__ float red[kThreads / 32];
-  const int64_t t = blockIdx.x;
+  __shared__ float red[6][kThreads / 32];
   const int tid = threadIdx.x;
-  const int64_t nvec = D / 8;
-  float f[kMaxVec][8];
-  float sum = 0.f;
+  const int nvec = static_cast<int>(D / 8);
+  V8 raw[NV], nxt[NV];
+  auto load_row = [&](int64_t row, V8 (&buf)[NV]) {
 #pragma unroll
-  for (int i = 0; i < kMaxVec; ++i) {
-    const int64_t vi = tid + static_cast<int64_t>(i) * kThreads;
-    if (vi < nvec) {
-      const V8 raw = *reinterpret_cast<const V8*>(x + t * ldx + vi * 8);
+    for (int i = 0; i < NV; ++i)
+      if (tid + i * kThreads < nvec) buf[i] = *reinterpret_cast<const V8*>(x + row * ldx + static_cast<int64_t>(tid + i * kThreads) * 8);
+  };
+  int64_t t = blockIdx.x;
+  if (t < rows) load_row(t, raw);
+  // CTAs stride over the rows; the next row's loads are issued before this row's three reductions
+  for (int it = 0; t < rows; t += gridDim.x, ++it) {
+    if (t + gridDim.x < rows) load_row(t + gridDim.x, nxt);
+    float* rbuf = red[(it & 1) * 3];
+    float f[NV][8];
+    float sum = 0.f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        f[i][j] = to_f<BF16>(raw.v[j]);
-        sum += f[i][j];
-      }
-    }
-  }
-  const float mean = block_sum(sum, red) / static_cast<float>(D);
-  float sq = 0.f;
+    for (int i = 0; i < NV; ++i)
+      if (tid + i * kThreads < nvec) {
 #pragma unroll
-  for (int i = 0; i < kMaxVec; ++i) {
-    const int64_t vi = tid + static_cast<int64_t>(i) * kThreads;
-    if (vi < nvec) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        f[i][j] -= mean;
-        sq = fmaf(f[i][j], f[i][j], sq);
-      }
-    }
-  }
-  const float rstd = rsqrtf(block_sum(sq, red) / static_cast<float>(D) + eps);
-  float amax = 0.f;
-#pragma unroll
-  for (int i = 0; i < kMaxVec; ++i) {
-    const int64_t vi = tid + static_cast<int64_t>(i) * kThreads;
-    if (vi < nvec) {
-      const int64_t n = vi * 8;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float v = f[i][j] * rstd;
-        if (w != nullptr) v = fmaf(v, w[n + j], b != nullptr ? b[n + j] : 0.f);
-        if (scale != nullptr) v = fmaf(v, 1.f + scale[n + j], shift[n + j]);
-        v = to_f<BF16>(from_f<BF16>(v));  // the tensor the reference materialises in the activation dtype
-        f[i][j] = v;
-        amax = fmaxf(amax, fabsf(v));
-      }
-      if (y != nullptr) {
-        V8 o;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) o.v[j] = from_f<BF16>(f[i][j]);
-        *reinterpret_cast<V8*>(y + t * ldy + n) = o;
-      }
-    }
-  }
-  if constexpr (QDT >= 0) {
-    amax = block_max(amax, red);
-    const float s = quant_scale<QDT>(amax, [](float v) { return to_f<BF16>(from_f<BF16>(v)); });
-    const float inv = __fdiv_rn(1.0f, s);
-    if (tid == 0) qscale[t] = s;
-#pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
-      const int64_t vi = tid + static_cast<int64_t>(i) * kThreads;
-      if (vi < nvec) {
-        uint32_t w0 = 0, w1 = 0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          w0 |= static_cast<uint32_t>(quant_one<QDT>(f[i][j], s, inv)) << (8 * j);
-          w1 |= static_cast<uint32_t>(quant_one<QDT>(f[i][4 + j], s, inv)) << (8 * j);
+        for (int j = 0; j < 8; ++j) {
+          f[i][j] = to_f<BF16>(raw[i].v[j]);
+          sum += f[i][j];
         }
-        *reinterpret_cast<uint2*>(q + t * D + vi * 8) = make_uint2(w0, w1);
       }
+    const float mean = block_sum(sum, rbuf) / static_cast<float>(D);
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      if (tid + i * kThreads < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          f[i][j] -= mean;
+          sq = fmaf(f[i][j], f[i][j], sq);
+        }
+      }
+    const float rstd = rsqrtf(block_sum(sq, rbuf + kThreads / 32) / static_cast<float>(D) + eps);
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      if (tid + i * kThreads < nvec) {
+        const int64_t n = static_cast<int64_t>(tid + i * kThreads) * 8;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float v = f[i][j] * rstd;
+          if (w != nullptr) v = fmaf(v, w[n + j], b != nullptr ? b[n + j] : 0.f);
+          if (scale != nullptr) v = fmaf(v, 1.f + scale[n + j], shift[n + j]);
+          v = to_f<BF16>(from_f<BF16>(v));  // the tensor the reference materialises in the activation dtype
+          f[i][j] = v;
+          amax = fmaxf(amax, fabsf(v));
+        }
+        if (y != nullptr) {
+          V8 o;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o.v[j] = from_f<BF16>(f[i][j]);
+          *reinterpret_cast<V8*>(y + t * ldy + n) = o;
+        }
+      }
+    if constexpr (QDT >= 0) {
+      amax = block_max(amax, rbuf + 2 * (kThreads / 32));
+      const float s = quant_scale<QDT>(amax, [](float v) { return to_f<BF16>(from_f<BF16>(v)); });
+      const float inv = __fdiv_rn(1.0f, s);
+      if (tid == 0) qscale[t] = s;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+        if (tid + i * kThreads < nvec) {
+          const uint32_t w0 = quant_four<QDT>(f[i][0], f[i][1], f[i][2], f[i][3], s, inv);
+          const uint32_t w1 = quant_four<QDT>(f[i][4], f[i][5], f[i][6], f[i][7], s, inv);
+          *reinterpret_cast<uint2*>(q + t * D + static_cast<int64_t>(tid + i * kThreads) * 8) = make_uint2(w0, w1);
+        }
     }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) raw[i] = nxt[i];
   }
 }
 
-template <bool BF16>
-int dispatch(int q_dtype, bool want_q, unsigned s, cudaStream_t st, const uint16_t* x, int64_t D, int64_t ldx,
-             const float* w, const float* b, const float* shift, const float* scale, float eps, uint16_t* y,
-             int64_t ldy, uint8_t* q, float* qscale) {
-  if (!want_q) {
-    ln_modulate_quant_kernel<BF16, -1><<<s, kThreads, 0, st>>>(x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
-  } else if (q_dtype == DAX_I8) {
-    ln_modulate_quant_kernel<BF16, DAX_I8><<<s, kThreads, 0, st>>>(x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
-  } else if (q_dtype == DAX_E4M3) {
-    ln_modulate_quant_kernel<BF16, DAX_E4M3><<<s, kThreads, 0, st>>>(x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
-  } else if (q_dtype == DAX_E5M2) {
-    ln_modulate_quant_kernel<BF16, DAX_E5M2><<<s, kThreads, 0, st>>>(x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
-  } else {
-    return fail(DAX_ERR_UNSUPPORTED, "layernorm_modulate_quant: q_dtype %d is not I8/E4M3/E5M2", q_dtype);
-  }
+template <bool BF16, int QDT, int NV>
+int launch(int64_t s, cudaStream_t st, const uint16_t* x, int64_t D, int64_t ldx, const float* w, const float* b,
+           const float* shift, const float* scale, float eps, uint16_t* y, int64_t ldy, uint8_t* q, float* qscale) {
+  // as many CTAs as fit on the GPU at once; each strides over the rows
+  int per_sm = 0;
+  DAX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ln_modulate_quant_kernel<BF16, QDT, NV>, kThreads, 0));
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>(s, static_cast<int64_t>(sm_count()) * std::max(per_sm, 1)));
+  ln_modulate_quant_kernel<BF16, QDT, NV><<<grid, kThreads, 0, st>>>(x, s, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
   DAX_CUDA(cudaGetLastError());
   return DAX_OK;
+}
+
+template <bool BF16, int QDT>
+int dispatch_nv(int64_t s, cudaStream_t st, const uint16_t* x, int64_t D, int64_t ldx, const float* w, const float* b,
+                const float* shift, const float* scale, float eps, uint16_t* y, int64_t ldy, uint8_t* q, float* qscale) {
+  const int64_t nv = (D / 8 + kThreads - 1) / kThreads;
+  if (nv <= 1) return launch<BF16, QDT, 1>(s, st, x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
+  if (nv <= 2) return launch<BF16, QDT, 2>(s, st, x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
+  if (nv <= 3) return launch<BF16, QDT, 3>(s, st, x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
+  return launch<BF16, QDT, kMaxVec>(s, st, x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
+}
+
+template <bool BF16>
+int dispatch(int q_dtype, bool want_q, int64_t s, cudaStream_t st, const uint16_t* x, int64_t D, int64_t ldx,
+             const float* w, const float* b, const float* shift, const float* scale, float eps, uint16_t* y,
+             int64_t ldy, uint8_t* q, float* qscale) {
+  if (!want_q) return dispatch_nv<BF16, -1>(s, st, x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
+  if (q_dtype == DAX_I8) return dispatch_nv<BF16, DAX_I8>(s, st, x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
+  if (q_dtype == DAX_E4M3) return dispatch_nv<BF16, DAX_E4M3>(s, st, x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
+  if (q_dtype == DAX_E5M2) return dispatch_nv<BF16, DAX_E5M2>(s, st, x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
+  return fail(DAX_ERR_UNSUPPORTED, "layernorm_modulate_quant: q_dtype %d is not I8/E4M3/E5M2", q_dtype);
 }
 
 }  // namespace
@@ -176,6 +193,6 @@ extern "C" int dax_layernorm_modulate_quant(const void* x, int dtype, int64_t s,
   uint16_t* yp = static_cast<uint16_t*>(y);
   uint8_t* qp = static_cast<uint8_t*>(q);
   if (dtype == DAX_BF16)
-    return dispatch<true>(q_dtype, q != nullptr, static_cast<unsigned>(s), st, xp, D, ldx, ln_weight, ln_bias, shift, scale, eps, yp, ldy, qp, qscale);
-  return dispatch<false>(q_dtype, q != nullptr, static_cast<unsigned>(s), st, xp, D, ldx, ln_weight, ln_bias, shift, scale, eps, yp, ldy, qp, qscale);
+    return dispatch<true>(q_dtype, q != nullptr, s, st, xp, D, ldx, ln_weight, ln_bias, shift, scale, eps, yp, ldy, qp, qscale);
+  return dispatch<false>(q_dtype, q != nullptr, s, st, xp, D, ldx, ln_weight, ln_bias, shift, scale, eps, yp, ldy, qp, qscale);
 }

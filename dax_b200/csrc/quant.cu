@@ -1,17 +1,21 @@
 // Per-token dynamic activation quantiser (absmax -> scale -> INT8 / FP8), one pass over HBM.
 //
 // HBM-bound: 2 (or 4) bytes read and 1 byte written per element plus 4 bytes per row.  A row is
-// read once with 128-bit loads into registers, reduced, and quantised from registers.  Rows are
-// mapped to a warp (short rows) or to a whole CTA (long rows) so that every thread has work.
+// read once with 128-bit loads into registers, reduced, and quantised from registers.  Short rows go one per
+// warp; rows of 257..2048 vectors go to CTAs that stride over the rows with the next row's loads already in
+// flight while the current row is reduced and converted (5.3-6.4 TB/s at 75,600 x 5120 / 13,824 on a B200);
+// longer rows are re-read from L2 for the second pass.
 //
 // Arithmetic follows the reference bit for bit (dax/quant/nn/dynamic/functional.py:124-135 and
 // dax/quant/nn/quantized/functional.py:11-20, evaluated eagerly):
 //   amax  = max |x|                       (exact in any precision)
 //   scale = round_to_input_dtype(amax / qmax), floored at fp32 eps, widened to fp32
 //   INT8: q = clamp(rint(x * (1.0f / scale)), -128, 127)    (multiply by the reciprocal)
-//   FP8 : q = round_nearest_even_to_fp8(clamp(x / scale))   (true division)
+//   FP8 : q = round_nearest_even_to_fp8(clamp(x / scale))   (true division, see div_rn_by)
 // All fp32 operations are the IEEE round-to-nearest intrinsics so that the compiler cannot
 // contract or approximate them.
+#include <algorithm>
+
 #include "quant_common.cuh"
 
 namespace dax {
@@ -41,6 +45,19 @@ template <typename T>
 struct alignas(16) Vec {
   T v[VecTraits<T>::N];
 };
+
+// One 16-byte vector of inputs -> N codes.
+template <typename T, int QDT>
+__device__ __forceinline__ void emit_vec(const Vec<T>& t, float s, float inv, uint8_t* dst) {
+  using V = VecTraits<T>;
+  const uint32_t w0 = quant_four<QDT>(V::to_f(t.v[0]), V::to_f(t.v[1]), V::to_f(t.v[2]), V::to_f(t.v[3]), s, inv);
+  if constexpr (V::N == 8) {
+    const uint32_t w1 = quant_four<QDT>(V::to_f(t.v[4]), V::to_f(t.v[5]), V::to_f(t.v[6]), V::to_f(t.v[7]), s, inv);
+    *reinterpret_cast<uint2*>(dst) = make_uint2(w0, w1);
+  } else {
+    *reinterpret_cast<uint32_t*>(dst) = w0;
+  }
+}
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
@@ -108,24 +125,7 @@ quant_rowwise_kernel(const T* __restrict__ x, int64_t M, int64_t K, int64_t ldx,
 
   uint8_t* qrow = q + row * K;
   auto emit = [&](const Vec<T>& t, int64_t vi) {
-    if constexpr (N == 8) {
-      uint2 o;
-      uint32_t w0 = 0, w1 = 0;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        w0 |= static_cast<uint32_t>(quant_one<QDT>(VecTraits<T>::to_f(t.v[j]), s, inv)) << (8 * j);
-        w1 |= static_cast<uint32_t>(quant_one<QDT>(VecTraits<T>::to_f(t.v[4 + j]), s, inv)) << (8 * j);
-      }
-      o.x = w0;
-      o.y = w1;
-      *reinterpret_cast<uint2*>(qrow + vi * 8) = o;
-    } else {
-      uint32_t w0 = 0;
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        w0 |= static_cast<uint32_t>(quant_one<QDT>(VecTraits<T>::to_f(t.v[j]), s, inv)) << (8 * j);
-      *reinterpret_cast<uint32_t*>(qrow + vi * 4) = w0;
-    }
+    emit_vec<T, QDT>(t, s, inv, qrow + vi * N);
   };
   if (cached) {
 #pragma unroll
@@ -138,10 +138,88 @@ quant_rowwise_kernel(const T* __restrict__ x, int64_t M, int64_t K, int64_t ldx,
   }
 }
 
+// Rows of 257..2048 vectors: CTAs stride over the rows and hold two rows in registers, the one being
+// quantised and the next one, whose loads are issued before the reduction of the current row: the reduction,
+// the barrier and the conversions run under the next row's memory latency.  NV = vectors per thread.
+template <typename T, int QDT, int NV>
+__global__ void __launch_bounds__(kThreads)
+quant_rows_pipelined_kernel(const T* __restrict__ x, int64_t M, int64_t K, int64_t ldx, int64_t col_group,
+                            int64_t group_stride, uint8_t* __restrict__ q, float* __restrict__ scale) {
+  constexpr int N = VecTraits<T>::N;
+  constexpr float qmax = QDT == DAX_I8 ? 127.f : (QDT == DAX_E4M3 ? 448.f : 57344.f);
+  __shared__ float red[2][kThreads / 32];
+  const int tid = threadIdx.x;
+  const int nvec = static_cast<int>(K / N);
+  // element offset of each of this thread's vectors inside a row (column-group addressing), fixed for all rows
+  int64_t off[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int64_t n = static_cast<int64_t>(tid + i * kThreads) * N;
+    const int64_t g = n / col_group;
+    off[i] = g * group_stride + (n - g * col_group);
+  }
+  auto load_row = [&](int64_t row, Vec<T> (&buf)[NV]) {
+    const T* base = x + row * ldx;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      if (tid + i * kThreads < nvec) buf[i] = *reinterpret_cast<const Vec<T>*>(base + off[i]);
+  };
+  Vec<T> cur[NV], nxt[NV];
+  int64_t row = blockIdx.x;
+  if (row < M) load_row(row, cur);
+  for (int it = 0; row < M; row += gridDim.x, ++it) {
+    if (row + gridDim.x < M) load_row(row + gridDim.x, nxt);
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      if (tid + i * kThreads < nvec) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) amax = fmaxf(amax, fabsf(VecTraits<T>::to_f(cur[i].v[j])));
+      }
+    amax = warp_max(amax);
+    float* r = red[it & 1];  // two buffers: one barrier per row is enough
+    if ((tid & 31) == 0) r[tid >> 5] = amax;
+    __syncthreads();
+    amax = r[0];
+#pragma unroll
+    for (int w = 1; w < kThreads / 32; ++w) amax = fmaxf(amax, r[w]);
+    float s = VecTraits<T>::round_trip(__fdiv_rn(amax, qmax));
+    s = fmaxf(s, 1.1920928955078125e-07f);
+    const float inv = __fdiv_rn(1.0f, s);
+    if (tid == 0) scale[row] = s;
+    uint8_t* qrow = q + row * K;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      if (tid + i * kThreads < nvec) emit_vec<T, QDT>(cur[i], s, inv, qrow + static_cast<int64_t>(tid + i * kThreads) * N);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) cur[i] = nxt[i];
+  }
+}
+
+template <typename T, int QDT, int NV>
+int launch_pipelined(const void* x, int64_t M, int64_t K, int64_t ldx, int64_t col_group, int64_t group_stride, void* q,
+                     float* scale, cudaStream_t st) {
+  int per_sm = 0;
+  DAX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quant_rows_pipelined_kernel<T, QDT, NV>, kThreads, 0));
+  const int64_t blocks = std::min<int64_t>(M, static_cast<int64_t>(sm_count()) * std::max(per_sm, 1));
+  quant_rows_pipelined_kernel<T, QDT, NV><<<static_cast<unsigned>(blocks), kThreads, 0, st>>>(
+      static_cast<const T*>(x), M, K, ldx, col_group, group_stride, static_cast<uint8_t*>(q), scale);
+  DAX_CUDA(cudaGetLastError());
+  return DAX_OK;
+}
+
 template <typename T, int QDT>
 int launch(const void* x, int64_t M, int64_t K, int64_t ldx, int64_t col_group, int64_t group_stride, void* q,
            float* scale, cudaStream_t st) {
   const int64_t nvec = K / VecTraits<T>::N;
+  if (nvec > 32 * kMaxVec && nvec <= kThreads * kMaxVec) {
+    const int nv = static_cast<int>((nvec + kThreads - 1) / kThreads);
+    if (nv <= 2) return launch_pipelined<T, QDT, 2>(x, M, K, ldx, col_group, group_stride, q, scale, st);
+    if (nv <= 3) return launch_pipelined<T, QDT, 3>(x, M, K, ldx, col_group, group_stride, q, scale, st);
+    if (nv <= 4) return launch_pipelined<T, QDT, 4>(x, M, K, ldx, col_group, group_stride, q, scale, st);
+    if (nv <= 6) return launch_pipelined<T, QDT, 6>(x, M, K, ldx, col_group, group_stride, q, scale, st);
+    return launch_pipelined<T, QDT, 8>(x, M, K, ldx, col_group, group_stride, q, scale, st);
+  }
   if (nvec <= 32 * kMaxVec) {
     constexpr int RPB = kThreads / 32;
     const int64_t blocks = (M + RPB - 1) / RPB;

@@ -6,20 +6,45 @@
 
 namespace dax {
 
+// x / s rounded to nearest, for a divisor whose correctly rounded reciprocal r = RN(1 / s) is at hand
+// (one per row): q0 = RN(x r), then one residual correction.  Both steps are fused multiply-adds, so the result
+// is the correctly rounded quotient wherever neither step leaves the normal range; quotients that small or
+// that large quantise to zero or saturate either way.  Requires s > 0.
+__device__ __forceinline__ float div_rn_by(float x, float s, float r) {
+  const float q0 = __fmul_rn(x, r);
+  const float q = __fmaf_rn(__fmaf_rn(-q0, s, x), r, q0);
+  // s > 0, so the quotient carries the sign of x; the correction step alone would turn -0 into +0
+  return __uint_as_float((__float_as_uint(q) & 0x7fffffffu) | (__float_as_uint(x) & 0x80000000u));
+}
+
+// Four values -> four codes packed into 32 bits (element 0 in the low byte).
+//   INT8: clamp(rint(x * inv_scale), -128, 127): one multiply and one saturating round-to-nearest-even conversion
+//   FP8 : round_nearest_even_to_fp8(clamp(x / scale)): the saturating conversion clamps to the largest finite code
 template <int QDT>
-__device__ __forceinline__ uint8_t quant_one(float x, float scale, float inv_scale) {
+__device__ __forceinline__ uint32_t quant_four(float a, float b, float c, float d, float scale, float inv_scale) {
   if constexpr (QDT == DAX_I8) {
-    float r = rintf(__fmul_rn(x, inv_scale));
-    r = fminf(fmaxf(r, -128.f), 127.f);
-    return static_cast<uint8_t>(static_cast<int8_t>(static_cast<int>(r)));
-  } else if constexpr (QDT == DAX_E4M3) {
-    float r = __fdiv_rn(x, scale);
-    r = fminf(fmaxf(r, -448.f), 448.f);
-    return static_cast<uint8_t>(__nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E4M3));
+    int32_t qa, qb, qc, qd;
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(qa) : "f"(__fmul_rn(a, inv_scale)));
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(qb) : "f"(__fmul_rn(b, inv_scale)));
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(qc) : "f"(__fmul_rn(c, inv_scale)));
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(qd) : "f"(__fmul_rn(d, inv_scale)));
+    uint32_t lo, hi, w;
+    asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(lo) : "r"(qa), "r"(qb));
+    asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(hi) : "r"(qc), "r"(qd));
+    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(w) : "r"(lo), "r"(hi));
+    return w;
   } else {
-    float r = __fdiv_rn(x, scale);
-    r = fminf(fmaxf(r, -57344.f), 57344.f);
-    return static_cast<uint8_t>(__nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E5M2));
+    const float qa = div_rn_by(a, scale, inv_scale), qb = div_rn_by(b, scale, inv_scale);
+    const float qc = div_rn_by(c, scale, inv_scale), qd = div_rn_by(d, scale, inv_scale);
+    uint16_t lo, hi;
+    if constexpr (QDT == DAX_E4M3) {
+      asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(qb), "f"(qa));
+      asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(qd), "f"(qc));
+    } else {
+      asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(qb), "f"(qa));
+      asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(qd), "f"(qc));
+    }
+    return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
   }
 }
 
