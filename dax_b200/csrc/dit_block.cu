@@ -59,8 +59,27 @@ ln_modulate_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D
                          const float* __restrict__ scale, float eps, uint16_t* __restrict__ y, int64_t ldy,
                          uint8_t* __restrict__ q, float* __restrict__ qscale) {
   __shared__ float red[6][kThreads / 32];
+  // The per-column vectors (fp32) are four times the bytes of a bf16 row: they are staged in shared memory once
+  // per CTA, as mul0/add0 (LayerNorm weight and bias) and mul1/add1 (1 + scale, shift), and read from there
+  // for every row.
+  extern __shared__ float4 vec_smem[];
+  float* mul0 = reinterpret_cast<float*>(vec_smem);
+  float* add0 = mul0 + (w != nullptr ? D : 0);
+  float* mul1 = add0 + (w != nullptr ? D : 0);
+  float* add1 = mul1 + (scale != nullptr ? D : 0);
   const int tid = threadIdx.x;
   const int nvec = static_cast<int>(D / 8);
+  for (int64_t n = tid; n < D; n += kThreads) {
+    if (w != nullptr) {
+      mul0[n] = w[n];
+      add0[n] = b != nullptr ? b[n] : 0.f;
+    }
+    if (scale != nullptr) {
+      mul1[n] = 1.f + scale[n];
+      add1[n] = shift[n];
+    }
+  }
+  __syncthreads();
   V8 raw[NV], nxt[NV];
   auto load_row = [&](int64_t row, V8 (&buf)[NV]) {
 #pragma unroll
@@ -73,16 +92,14 @@ ln_modulate_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D
   for (int it = 0; t < rows; t += gridDim.x, ++it) {
     if (t + gridDim.x < rows) load_row(t + gridDim.x, nxt);
     float* rbuf = red[(it & 1) * 3];
-    float f[NV][8];
+    // The row stays packed (16-bit) in registers and is widened again in each pass: a third of the registers
+    // of an fp32 copy, which is what lets four CTAs share an SM.
     float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i)
       if (tid + i * kThreads < nvec) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          f[i][j] = to_f<BF16>(raw[i].v[j]);
-          sum += f[i][j];
-        }
+        for (int j = 0; j < 8; ++j) sum += to_f<BF16>(raw[i].v[j]);
       }
     const float mean = block_sum(sum, rbuf) / static_cast<float>(D);
     float sq = 0.f;
@@ -91,8 +108,8 @@ ln_modulate_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D
       if (tid + i * kThreads < nvec) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          f[i][j] -= mean;
-          sq = fmaf(f[i][j], f[i][j], sq);
+          const float c = to_f<BF16>(raw[i].v[j]) - mean;
+          sq = fmaf(c, c, sq);
         }
       }
     const float rstd = rsqrtf(block_sum(sq, rbuf + kThreads / 32) / static_cast<float>(D) + eps);
@@ -101,21 +118,29 @@ ln_modulate_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D
     for (int i = 0; i < NV; ++i)
       if (tid + i * kThreads < nvec) {
         const int64_t n = static_cast<int64_t>(tid + i * kThreads) * 8;
+        float m0[8], a0[8], m1[8], a1[8];
+        if (w != nullptr) {
+          *reinterpret_cast<float4*>(&m0[0]) = *reinterpret_cast<const float4*>(mul0 + n);
+          *reinterpret_cast<float4*>(&m0[4]) = *reinterpret_cast<const float4*>(mul0 + n + 4);
+          *reinterpret_cast<float4*>(&a0[0]) = *reinterpret_cast<const float4*>(add0 + n);
+          *reinterpret_cast<float4*>(&a0[4]) = *reinterpret_cast<const float4*>(add0 + n + 4);
+        }
+        if (scale != nullptr) {
+          *reinterpret_cast<float4*>(&m1[0]) = *reinterpret_cast<const float4*>(mul1 + n);
+          *reinterpret_cast<float4*>(&m1[4]) = *reinterpret_cast<const float4*>(mul1 + n + 4);
+          *reinterpret_cast<float4*>(&a1[0]) = *reinterpret_cast<const float4*>(add1 + n);
+          *reinterpret_cast<float4*>(&a1[4]) = *reinterpret_cast<const float4*>(add1 + n + 4);
+        }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          float v = f[i][j] * rstd;
-          if (w != nullptr) v = fmaf(v, w[n + j], b != nullptr ? b[n + j] : 0.f);
-          if (scale != nullptr) v = fmaf(v, 1.f + scale[n + j], shift[n + j]);
-          v = to_f<BF16>(from_f<BF16>(v));  // the tensor the reference materialises in the activation dtype
-          f[i][j] = v;
-          amax = fmaxf(amax, fabsf(v));
+          float v = (to_f<BF16>(raw[i].v[j]) - mean) * rstd;
+          if (w != nullptr) v = fmaf(v, m0[j], a0[j]);
+          if (scale != nullptr) v = fmaf(v, m1[j], a1[j]);
+          // the tensor the reference materialises in the activation dtype; it replaces the input in registers
+          raw[i].v[j] = from_f<BF16>(v);
+          amax = fmaxf(amax, fabsf(to_f<BF16>(raw[i].v[j])));
         }
-        if (y != nullptr) {
-          V8 o;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o.v[j] = from_f<BF16>(f[i][j]);
-          *reinterpret_cast<V8*>(y + t * ldy + n) = o;
-        }
+        if (y != nullptr) *reinterpret_cast<V8*>(y + t * ldy + n) = raw[i];
       }
     if constexpr (QDT >= 0) {
       amax = block_max(amax, rbuf + 2 * (kThreads / 32));
@@ -125,8 +150,10 @@ ln_modulate_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D
 #pragma unroll
       for (int i = 0; i < NV; ++i)
         if (tid + i * kThreads < nvec) {
-          const uint32_t w0 = quant_four<QDT>(f[i][0], f[i][1], f[i][2], f[i][3], s, inv);
-          const uint32_t w1 = quant_four<QDT>(f[i][4], f[i][5], f[i][6], f[i][7], s, inv);
+          const uint32_t w0 = quant_four<QDT>(to_f<BF16>(raw[i].v[0]), to_f<BF16>(raw[i].v[1]), to_f<BF16>(raw[i].v[2]),
+                                              to_f<BF16>(raw[i].v[3]), s, inv);
+          const uint32_t w1 = quant_four<QDT>(to_f<BF16>(raw[i].v[4]), to_f<BF16>(raw[i].v[5]), to_f<BF16>(raw[i].v[6]),
+                                              to_f<BF16>(raw[i].v[7]), s, inv);
           *reinterpret_cast<uint2*>(q + t * D + static_cast<int64_t>(tid + i * kThreads) * 8) = make_uint2(w0, w1);
         }
     }
@@ -140,9 +167,13 @@ int launch(int64_t s, cudaStream_t st, const uint16_t* x, int64_t D, int64_t ldx
            const float* shift, const float* scale, float eps, uint16_t* y, int64_t ldy, uint8_t* q, float* qscale) {
   // as many CTAs as fit on the GPU at once; each strides over the rows
   int per_sm = 0;
-  DAX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ln_modulate_quant_kernel<BF16, QDT, NV>, kThreads, 0));
+  const size_t smem = static_cast<size_t>(D) * sizeof(float) * ((w != nullptr ? 2 : 0) + (scale != nullptr ? 2 : 0));
+  if (smem > 48 * 1024)
+    DAX_CUDA(cudaFuncSetAttribute(ln_modulate_quant_kernel<BF16, QDT, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(smem)));
+  DAX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ln_modulate_quant_kernel<BF16, QDT, NV>, kThreads, smem));
   const unsigned grid = static_cast<unsigned>(std::min<int64_t>(s, static_cast<int64_t>(sm_count()) * std::max(per_sm, 1)));
-  ln_modulate_quant_kernel<BF16, QDT, NV><<<grid, kThreads, 0, st>>>(x, s, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
+  ln_modulate_quant_kernel<BF16, QDT, NV><<<grid, kThreads, smem, st>>>(x, s, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
   DAX_CUDA(cudaGetLastError());
   return DAX_OK;
 }

@@ -2,13 +2,16 @@
 // one pass over HBM (2 bytes read + 2 bytes written per element; the rotary tables and the norm
 // weight stay in L2).
 //
-// One CTA per token row.  The row is read once into registers with 128-bit loads.  The sum of
+// CTAs stride over the token rows.  A row is read once into registers with 128-bit loads, and the next
+// row's loads are issued before the current row is normalised and rotated.  The sum of
 // squares either comes from the per-column-tile partial sums the projection GEMM's epilogue wrote
 // (summed in tile order, so the result does not depend on scheduling) or is reduced here.
 // The normalised value is rounded to the tensor dtype before the rotation, like the tensor the
 // reference materialises between its RMSNorm module and apply_rotary_emb
 // (dax/adapters/wan/attn_adapter.py:108-109,164-173); the rotation itself runs in fp32 on
 // interleaved pairs (x[2i], x[2i+1]) * (cos_i + j sin_i) and is rounded once.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace dax {
@@ -32,91 +35,126 @@ __device__ __forceinline__ uint16_t from_f(float f) {
   else return __half_as_ushort(__float2half_rn(f));
 }
 
-template <bool BF16>
-__global__ void __launch_bounds__(kThreads)
+// NV = 16-byte vectors per thread (rows of up to NV * 2048 elements)
+template <bool BF16, int NV>
+__global__ void __launch_bounds__(kThreads, NV <= 3 ? 3 : 2)
 rmsnorm_rope_pack_kernel(const uint16_t* __restrict__ x, int64_t s, int64_t D, int64_t ldx,
                          const float* __restrict__ row_sumsq, int64_t n_partials, int do_norm,
                          const uint16_t* __restrict__ w, float eps, const float* __restrict__ rope_cos,
                          const float* __restrict__ rope_sin, int64_t token_offset, uint16_t* __restrict__ out,
                          int64_t ldo, int64_t col_group, int64_t group_stride) {
-  __shared__ float red[kThreads / 32];
-  const int64_t t = blockIdx.x;
-  const int tid = threadIdx.x;
-  const int64_t nvec = D / 8;
-
-  V8 regs[kMaxVec];
-  float ss = 0.f;
-#pragma unroll
-  for (int i = 0; i < kMaxVec; ++i) {
-    const int64_t vi = tid + static_cast<int64_t>(i) * kThreads;
-    if (vi < nvec) {
-      regs[i] = *reinterpret_cast<const V8*>(x + t * ldx + vi * 8);
-      if (do_norm && row_sumsq == nullptr) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float f = to_f<BF16>(regs[i].v[j]);
-          ss = fmaf(f, f, ss);
-        }
-      }
-    }
-  }
-  float rstd = 1.f;
-  if (do_norm) {
-    if (row_sumsq != nullptr) {
-      ss = 0.f;
-      for (int64_t j = 0; j < n_partials; ++j) ss += row_sumsq[t * n_partials + j];
-    } else {
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      if ((tid & 31) == 0) red[tid >> 5] = ss;
-      __syncthreads();
-      ss = 0.f;
-#pragma unroll
-      for (int k = 0; k < kThreads / 32; ++k) ss += red[k];
-    }
-    rstd = rsqrtf(ss / static_cast<float>(D) + eps);
-  }
-
+  __shared__ float red[2][kThreads / 32];
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int nvec = static_cast<int>(D / 8);
   const bool rope = rope_cos != nullptr;
-  const int64_t gtok = token_offset + t;
+
+  // per-thread constants of the row layout: output offset of each vector and the norm weight
+  int64_t out_off[NV];
+  V8 wv[NV];
 #pragma unroll
-  for (int i = 0; i < kMaxVec; ++i) {
-    const int64_t vi = tid + static_cast<int64_t>(i) * kThreads;
-    if (vi < nvec) {
-      const int64_t n = vi * 8;
-      float f[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) f[j] = to_f<BF16>(regs[i].v[j]);
-      if (do_norm) {
-        V8 wv;
-        if (w != nullptr) wv = *reinterpret_cast<const V8*>(w + n);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float y = f[j] * rstd;
-          if (w != nullptr) y *= to_f<BF16>(wv.v[j]);
-          f[j] = to_f<BF16>(from_f<BF16>(y));
-        }
-      }
-      if (rope) {
-        const int pair0 = static_cast<int>((n & 127) >> 1);  // 4 consecutive pairs of one head
-        const float4 c4 = *reinterpret_cast<const float4*>(rope_cos + gtok * 64 + pair0);
-        const float4 s4 = *reinterpret_cast<const float4*>(rope_sin + gtok * 64 + pair0);
-        const float cs[4] = {c4.x, c4.y, c4.z, c4.w};
-        const float sn[4] = {s4.x, s4.y, s4.z, s4.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float a = f[2 * j], b = f[2 * j + 1];
-          f[2 * j] = a * cs[j] - b * sn[j];
-          f[2 * j + 1] = a * sn[j] + b * cs[j];
-        }
-      }
-      V8 o;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) o.v[j] = from_f<BF16>(f[j]);
-      const int64_t g = n / col_group;
-      *reinterpret_cast<V8*>(out + g * group_stride + t * ldo + (n - g * col_group)) = o;
-    }
+  for (int i = 0; i < NV; ++i) {
+    const int64_t n = static_cast<int64_t>(tid + i * kThreads) * 8;
+    const int64_t g = n / col_group;
+    out_off[i] = g * group_stride + (n - g * col_group);
+    if (do_norm && w != nullptr && tid + i * kThreads < nvec) wv[i] = *reinterpret_cast<const V8*>(w + n);
   }
+  auto load_row = [&](int64_t row, V8 (&buf)[NV]) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      if (tid + i * kThreads < nvec) buf[i] = *reinterpret_cast<const V8*>(x + row * ldx + static_cast<int64_t>(tid + i * kThreads) * 8);
+  };
+  V8 regs[NV], nxt[NV];
+  int64_t t = blockIdx.x;
+  if (t < s) load_row(t, regs);
+  // CTAs stride over the rows with the next row's loads in flight
+  for (int it = 0; t < s; t += gridDim.x, ++it) {
+    if (t + gridDim.x < s) load_row(t + gridDim.x, nxt);
+    float rstd = 1.f;
+    if (do_norm) {
+      float ss = 0.f;
+      if (row_sumsq != nullptr) {
+        // the GEMM's per-tile partial sums, added in an order fixed by the lane number alone
+        for (int64_t j = lane; j < n_partials; j += 32) ss += row_sumsq[t * n_partials + j];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      } else {
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+          if (tid + i * kThreads < nvec) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float f = to_f<BF16>(regs[i].v[j]);
+              ss = fmaf(f, f, ss);
+            }
+          }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        float* r = red[it & 1];  // two buffers: one barrier per row
+        if (lane == 0) r[tid >> 5] = ss;
+        __syncthreads();
+        ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < kThreads / 32; ++k) ss += r[k];
+      }
+      rstd = rsqrtf(ss / static_cast<float>(D) + eps);
+    }
+    const int64_t gtok = token_offset + t;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      if (tid + i * kThreads < nvec) {
+        const int64_t n = static_cast<int64_t>(tid + i * kThreads) * 8;
+        float f[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = to_f<BF16>(regs[i].v[j]);
+        if (do_norm) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float y = f[j] * rstd;
+            if (w != nullptr) y *= to_f<BF16>(wv[i].v[j]);
+            f[j] = to_f<BF16>(from_f<BF16>(y));
+          }
+        }
+        if (rope) {
+          const int pair0 = static_cast<int>((n & 127) >> 1);  // 4 consecutive pairs of one head
+          const float4 c4 = *reinterpret_cast<const float4*>(rope_cos + gtok * 64 + pair0);
+          const float4 s4 = *reinterpret_cast<const float4*>(rope_sin + gtok * 64 + pair0);
+          const float cs[4] = {c4.x, c4.y, c4.z, c4.w};
+          const float sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float a = f[2 * j], b = f[2 * j + 1];
+            f[2 * j] = a * cs[j] - b * sn[j];
+            f[2 * j + 1] = a * sn[j] + b * cs[j];
+          }
+        }
+        V8 o;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o.v[j] = from_f<BF16>(f[j]);
+        *reinterpret_cast<V8*>(out + out_off[i] + t * ldo) = o;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) regs[i] = nxt[i];
+  }
+}
+
+template <bool BF16, int NV, typename... Args>
+int launch(int64_t s, cudaStream_t st, Args... args) {
+  int per_sm = 0;
+  DAX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rmsnorm_rope_pack_kernel<BF16, NV>, kThreads, 0));
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>(s, static_cast<int64_t>(sm_count()) * std::max(per_sm, 1)));
+  rmsnorm_rope_pack_kernel<BF16, NV><<<grid, kThreads, 0, st>>>(args...);
+  DAX_CUDA(cudaGetLastError());
+  return DAX_OK;
+}
+
+template <bool BF16, typename... Args>
+int dispatch(int64_t s, int64_t D, cudaStream_t st, Args... args) {
+  const int64_t nv = (D / 8 + kThreads - 1) / kThreads;
+  if (nv <= 1) return launch<BF16, 1>(s, st, args...);
+  if (nv <= 2) return launch<BF16, 2>(s, st, args...);
+  if (nv <= 3) return launch<BF16, 3>(s, st, args...);
+  return launch<BF16, kMaxVec>(s, st, args...);
 }
 
 }  // namespace
@@ -149,11 +187,8 @@ extern "C" int dax_rmsnorm_rope_pack(const void* x, int dtype, int64_t s, int64_
   const uint16_t* wp = static_cast<const uint16_t*>(norm_weight);
   uint16_t* op = static_cast<uint16_t*>(out);
   if (dtype == DAX_BF16)
-    rmsnorm_rope_pack_kernel<true><<<static_cast<unsigned>(s), kThreads, 0, st>>>(
-        xp, s, D, ldx, row_sumsq, n_partials, do_norm, wp, eps, rope_cos, rope_sin, token_offset, op, ldo, col_group, group_stride);
-  else
-    rmsnorm_rope_pack_kernel<false><<<static_cast<unsigned>(s), kThreads, 0, st>>>(
-        xp, s, D, ldx, row_sumsq, n_partials, do_norm, wp, eps, rope_cos, rope_sin, token_offset, op, ldo, col_group, group_stride);
-  DAX_CUDA(cudaGetLastError());
-  return DAX_OK;
+    return dispatch<true>(s, D, st, xp, s, D, ldx, row_sumsq, n_partials, do_norm, wp, eps, rope_cos, rope_sin, token_offset,
+                          op, ldo, col_group, group_stride);
+  return dispatch<false>(s, D, st, xp, s, D, ldx, row_sumsq, n_partials, do_norm, wp, eps, rope_cos, rope_sin, token_offset,
+                         op, ldo, col_group, group_stride);
 }
