@@ -223,11 +223,15 @@ def main():
 
     gx = torch.Generator().manual_seed(99)
     if dit:
-        assert tokens == TOKENS, "--tokens applies to --workload hotpath only"
-        x_host = torch.randn(LATENT, generator=gx).to(torch.bfloat16).pin_memory()  # replicated latent, split inside
+        latent = LATENT
+        if tokens != TOKENS:  # reduced case for profiler captures: 4 frames of a square latent
+            side = int(round((tokens // 4) ** 0.5))
+            assert 4 * side * side == tokens, "--tokens for the dit workload must be 4 * n^2"
+            latent = (1, 16, 4, 2 * side, 2 * side)
+        x_host = torch.randn(latent, generator=gx).to(torch.bfloat16).pin_memory()  # replicated latent, split inside
         text = torch.randn(1, TEXT_TOKENS, TEXT_DIM, generator=gx).to(torch.bfloat16).to(dev)
         timestep = torch.randint(0, 1000, (1,), generator=gx).to(dev)
-        y_host = torch.empty(LATENT, dtype=torch.bfloat16).pin_memory()
+        y_host = torch.empty(latent, dtype=torch.bfloat16).pin_memory()
         h2d_bytes = d2h_bytes = x_host.numel() * 2 * world
     else:
         rope = wan_rope_table(GRID if tokens == TOKENS else (1, 1, tokens), device=dev)

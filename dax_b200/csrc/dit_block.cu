@@ -17,7 +17,7 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kMaxVec = 4;  // rows up to 8192 elements
 
-struct alignas(16) V8 { uint16_t v[8]; };
+struct alignas(16) V8 { uint32_t w[4]; };  // eight 16-bit elements, two per word
 
 template <bool BF16> __device__ __forceinline__ float to_f(uint16_t u) {
   if constexpr (BF16) return __bfloat162float(__ushort_as_bfloat16(u));
@@ -53,7 +53,7 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 
 // QDT < 0: no quantised output.  NV = 16-byte vectors per thread (rows of up to NV * 2048 elements).
 template <bool BF16, int QDT, int NV>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, NV <= 3 ? 3 : 2)
 ln_modulate_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D, int64_t ldx, const float* __restrict__ w,
                          const float* __restrict__ b, const float* __restrict__ shift,
                          const float* __restrict__ scale, float eps, uint16_t* __restrict__ y, int64_t ldy,
@@ -99,7 +99,12 @@ ln_modulate_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D
     for (int i = 0; i < NV; ++i)
       if (tid + i * kThreads < nvec) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) sum += to_f<BF16>(raw[i].v[j]);
+        for (int k = 0; k < 4; ++k) {
+          float lo, hi;
+          unpack2<BF16>(raw[i].w[k], lo, hi);
+          sum += lo;
+          sum += hi;
+        }
       }
     const float mean = block_sum(sum, rbuf) / static_cast<float>(D);
     float sq = 0.f;
@@ -107,13 +112,17 @@ ln_modulate_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D
     for (int i = 0; i < NV; ++i)
       if (tid + i * kThreads < nvec) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float c = to_f<BF16>(raw[i].v[j]) - mean;
-          sq = fmaf(c, c, sq);
+        for (int k = 0; k < 4; ++k) {
+          float lo, hi;
+          unpack2<BF16>(raw[i].w[k], lo, hi);
+          lo -= mean;
+          hi -= mean;
+          sq = fmaf(lo, lo, sq);
+          sq = fmaf(hi, hi, sq);
         }
       }
     const float rstd = rsqrtf(block_sum(sq, rbuf + kThreads / 32) / static_cast<float>(D) + eps);
-    float amax = 0.f;
+    uint32_t amax2 = 0u;
 #pragma unroll
     for (int i = 0; i < NV; ++i)
       if (tid + i * kThreads < nvec) {
@@ -132,28 +141,37 @@ ln_modulate_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D
           *reinterpret_cast<float4*>(&a1[4]) = *reinterpret_cast<const float4*>(add1 + n + 4);
         }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float v = (to_f<BF16>(raw[i].v[j]) - mean) * rstd;
-          if (w != nullptr) v = fmaf(v, m0[j], a0[j]);
-          if (scale != nullptr) v = fmaf(v, m1[j], a1[j]);
+        for (int k = 0; k < 4; ++k) {
+          float v[2];
+          unpack2<BF16>(raw[i].w[k], v[0], v[1]);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int j = 2 * k + h;
+            v[h] = (v[h] - mean) * rstd;
+            if (w != nullptr) v[h] = fmaf(v[h], m0[j], a0[j]);
+            if (scale != nullptr) v[h] = fmaf(v[h], m1[j], a1[j]);
+          }
           // the tensor the reference materialises in the activation dtype; it replaces the input in registers
-          raw[i].v[j] = from_f<BF16>(v);
-          amax = fmaxf(amax, fabsf(to_f<BF16>(raw[i].v[j])));
+          raw[i].w[k] = pack2_rn<BF16>(v[0], v[1]);
+          amax2 = absmax2<BF16>(amax2, raw[i].w[k]);
         }
         if (y != nullptr) *reinterpret_cast<V8*>(y + t * ldy + n) = raw[i];
       }
     if constexpr (QDT >= 0) {
-      amax = block_max(amax, rbuf + 2 * (kThreads / 32));
+      float alo, ahi;
+      unpack2<BF16>(amax2, alo, ahi);
+      const float amax = block_max(fmaxf(alo, ahi), rbuf + 2 * (kThreads / 32));
       const float s = quant_scale<QDT>(amax, [](float v) { return to_f<BF16>(from_f<BF16>(v)); });
       const float inv = __fdiv_rn(1.0f, s);
       if (tid == 0) qscale[t] = s;
 #pragma unroll
       for (int i = 0; i < NV; ++i)
         if (tid + i * kThreads < nvec) {
-          const uint32_t w0 = quant_four<QDT>(to_f<BF16>(raw[i].v[0]), to_f<BF16>(raw[i].v[1]), to_f<BF16>(raw[i].v[2]),
-                                              to_f<BF16>(raw[i].v[3]), s, inv);
-          const uint32_t w1 = quant_four<QDT>(to_f<BF16>(raw[i].v[4]), to_f<BF16>(raw[i].v[5]), to_f<BF16>(raw[i].v[6]),
-                                              to_f<BF16>(raw[i].v[7]), s, inv);
+          float f[8];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) unpack2<BF16>(raw[i].w[k], f[2 * k], f[2 * k + 1]);
+          const uint32_t w0 = quant_four<QDT>(f[0], f[1], f[2], f[3], s, inv);
+          const uint32_t w1 = quant_four<QDT>(f[4], f[5], f[6], f[7], s, inv);
           *reinterpret_cast<uint2*>(q + t * D + static_cast<int64_t>(tid + i * kThreads) * 8) = make_uint2(w0, w1);
         }
     }

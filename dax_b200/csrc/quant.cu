@@ -27,35 +27,67 @@ constexpr int kMaxVec = 8;  // 16-byte vectors cached per thread
 template <typename T> struct VecTraits;
 template <> struct VecTraits<__nv_bfloat16> {
   static constexpr int N = 8;
-  __device__ static float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static constexpr bool IS16 = true, BF16 = true;
   __device__ static float round_trip(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
 };
 template <> struct VecTraits<__half> {
   static constexpr int N = 8;
-  __device__ static float to_f(__half v) { return __half2float(v); }
+  static constexpr bool IS16 = true, BF16 = false;
   __device__ static float round_trip(float f) { return __half2float(__float2half_rn(f)); }
 };
 template <> struct VecTraits<float> {
   static constexpr int N = 4;
-  __device__ static float to_f(float v) { return v; }
+  static constexpr bool IS16 = false, BF16 = false;
   __device__ static float round_trip(float f) { return f; }
 };
 
+// 16 bytes of a row: 8 sixteen-bit elements (two per word) or 4 fp32 elements
 template <typename T>
 struct alignas(16) Vec {
-  T v[VecTraits<T>::N];
+  uint32_t w[4];
+};
+
+// Running |.|-maximum of a thread: packed for 16-bit inputs (exact: the maximum of bf16 values is a bf16 value)
+template <typename T>
+struct AbsMax {
+  uint32_t packed = 0u;
+  float f = 0.f;
+  __device__ __forceinline__ void add(const Vec<T>& t) {
+    using V = VecTraits<T>;
+    if constexpr (V::IS16) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) packed = absmax2<V::BF16>(packed, t.w[k]);
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) f = fmaxf(f, fabsf(__uint_as_float(t.w[k])));
+    }
+  }
+  __device__ __forceinline__ float value() const {
+    using V = VecTraits<T>;
+    if constexpr (V::IS16) {
+      float lo, hi;
+      unpack2<V::BF16>(packed, lo, hi);
+      return fmaxf(lo, hi);
+    } else {
+      return f;
+    }
+  }
 };
 
 // One 16-byte vector of inputs -> N codes.
 template <typename T, int QDT>
 __device__ __forceinline__ void emit_vec(const Vec<T>& t, float s, float inv, uint8_t* dst) {
   using V = VecTraits<T>;
-  const uint32_t w0 = quant_four<QDT>(V::to_f(t.v[0]), V::to_f(t.v[1]), V::to_f(t.v[2]), V::to_f(t.v[3]), s, inv);
-  if constexpr (V::N == 8) {
-    const uint32_t w1 = quant_four<QDT>(V::to_f(t.v[4]), V::to_f(t.v[5]), V::to_f(t.v[6]), V::to_f(t.v[7]), s, inv);
+  if constexpr (V::IS16) {
+    float f[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) unpack2<V::BF16>(t.w[k], f[2 * k], f[2 * k + 1]);
+    const uint32_t w0 = quant_four<QDT>(f[0], f[1], f[2], f[3], s, inv);
+    const uint32_t w1 = quant_four<QDT>(f[4], f[5], f[6], f[7], s, inv);
     *reinterpret_cast<uint2*>(dst) = make_uint2(w0, w1);
   } else {
-    *reinterpret_cast<uint32_t*>(dst) = w0;
+    *reinterpret_cast<uint32_t*>(dst) = quant_four<QDT>(__uint_as_float(t.w[0]), __uint_as_float(t.w[1]),
+                                                        __uint_as_float(t.w[2]), __uint_as_float(t.w[3]), s, inv);
   }
 }
 
@@ -83,7 +115,7 @@ quant_rowwise_kernel(const T* __restrict__ x, int64_t M, int64_t K, int64_t ldx,
   const bool cached = nvec <= static_cast<int64_t>(TPR) * kMaxVec;
 
   Vec<T> regs[kMaxVec];
-  float amax = 0.f;
+  AbsMax<T> am;
   auto src = [&](int64_t vi) -> const Vec<T>* {
     const int64_t n = vi * N;
     const int64_t g = n / col_group;
@@ -96,19 +128,16 @@ quant_rowwise_kernel(const T* __restrict__ x, int64_t M, int64_t K, int64_t ldx,
         const int64_t vi = sub + static_cast<int64_t>(i) * TPR;
         if (vi < nvec) {
           regs[i] = *src(vi);
-#pragma unroll
-          for (int j = 0; j < N; ++j) amax = fmaxf(amax, fabsf(VecTraits<T>::to_f(regs[i].v[j])));
+          am.add(regs[i]);
         }
       }
     } else {
       for (int64_t vi = sub; vi < nvec; vi += TPR) {
-        Vec<T> t = *src(vi);
-#pragma unroll
-        for (int j = 0; j < N; ++j) amax = fmaxf(amax, fabsf(VecTraits<T>::to_f(t.v[j])));
+        am.add(*src(vi));
       }
     }
   }
-  amax = warp_max(amax);
+  float amax = warp_max(am.value());
   if constexpr (TPR > 32) {
     if ((tid & 31) == 0) red[tid >> 5] = amax;
     __syncthreads();
@@ -169,14 +198,11 @@ quant_rows_pipelined_kernel(const T* __restrict__ x, int64_t M, int64_t K, int64
   if (row < M) load_row(row, cur);
   for (int it = 0; row < M; row += gridDim.x, ++it) {
     if (row + gridDim.x < M) load_row(row + gridDim.x, nxt);
-    float amax = 0.f;
+    AbsMax<T> am;
 #pragma unroll
     for (int i = 0; i < NV; ++i)
-      if (tid + i * kThreads < nvec) {
-#pragma unroll
-        for (int j = 0; j < N; ++j) amax = fmaxf(amax, fabsf(VecTraits<T>::to_f(cur[i].v[j])));
-      }
-    amax = warp_max(amax);
+      if (tid + i * kThreads < nvec) am.add(cur[i]);
+    float amax = warp_max(am.value());
     float* r = red[it & 1];  // two buffers: one barrier per row is enough
     if ((tid & 31) == 0) r[tid >> 5] = amax;
     __syncthreads();

@@ -2,9 +2,42 @@
 // (quant.cu, dit_block.cu).  Bit-for-bit the reference's eager arithmetic
 // (dax/quant/nn/dynamic/functional.py:124-135, dax/quant/nn/quantized/functional.py:11-20).
 #pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 
 namespace dax {
+
+// Two 16-bit floats in one 32-bit word (element 0 in the low half) <-> two fp32, and the packed |.|-max: one
+// instruction per element or per pair instead of an extract-and-convert sequence per element.
+template <bool BF16>
+__device__ __forceinline__ void unpack2(uint32_t w, float& lo, float& hi) {
+  if constexpr (BF16) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xffff0000u);
+  } else {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+    lo = f.x;
+    hi = f.y;
+  }
+}
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2_rn(float lo, float hi) {  // round to nearest even
+  uint32_t r;
+  if constexpr (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// acc = max(acc, |w|) on both halves; acc starts at 0.  A NaN element is ignored, as fmaxf does.
+template <bool BF16>
+__device__ __forceinline__ uint32_t absmax2(uint32_t acc, uint32_t w) {
+  uint32_t r;
+  const uint32_t a = w & 0x7fff7fffu;
+  if constexpr (BF16) asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(acc), "r"(a));
+  else asm("max.f16x2 %0, %1, %2;" : "=r"(r) : "r"(acc), "r"(a));
+  return r;
+}
 
 // x / s rounded to nearest, for a divisor whose correctly rounded reciprocal r = RN(1 / s) is at hand
 // (one per row): q0 = RN(x r), then one residual correction.  Both steps are fused multiply-adds, so the result

@@ -12,7 +12,7 @@
 // interleaved pairs (x[2i], x[2i+1]) * (cos_i + j sin_i) and is rounded once.
 #include <algorithm>
 
-#include "common.cuh"
+#include "quant_common.cuh"
 
 namespace dax {
 namespace {
@@ -21,7 +21,7 @@ constexpr int kThreads = 256;
 constexpr int kMaxVec = 4;  // 8-element vectors per thread: rows up to 8192 elements
 
 struct alignas(16) V8 {
-  uint16_t v[8];
+  uint32_t w[4];  // eight 16-bit elements, two per word
 };
 
 template <bool BF16>
@@ -82,9 +82,11 @@ rmsnorm_rope_pack_kernel(const uint16_t* __restrict__ x, int64_t s, int64_t D, i
         for (int i = 0; i < NV; ++i)
           if (tid + i * kThreads < nvec) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float f = to_f<BF16>(regs[i].v[j]);
-              ss = fmaf(f, f, ss);
+            for (int k = 0; k < 4; ++k) {
+              float lo, hi;
+              unpack2<BF16>(regs[i].w[k], lo, hi);
+              ss = fmaf(lo, lo, ss);
+              ss = fmaf(hi, hi, ss);
             }
           }
 #pragma unroll
@@ -105,13 +107,19 @@ rmsnorm_rope_pack_kernel(const uint16_t* __restrict__ x, int64_t s, int64_t D, i
         const int64_t n = static_cast<int64_t>(tid + i * kThreads) * 8;
         float f[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = to_f<BF16>(regs[i].v[j]);
+        for (int k = 0; k < 4; ++k) unpack2<BF16>(regs[i].w[k], f[2 * k], f[2 * k + 1]);
         if (do_norm) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float y = f[j] * rstd;
-            if (w != nullptr) y *= to_f<BF16>(wv[i].v[j]);
-            f[j] = to_f<BF16>(from_f<BF16>(y));
+          for (int k = 0; k < 4; ++k) {
+            float y0 = f[2 * k] * rstd, y1 = f[2 * k + 1] * rstd;
+            if (w != nullptr) {
+              float w0, w1;
+              unpack2<BF16>(wv[i].w[k], w0, w1);
+              y0 *= w0;
+              y1 *= w1;
+            }
+            // rounded to the tensor dtype, as the reference's RMSNorm module returns it
+            unpack2<BF16>(pack2_rn<BF16>(y0, y1), f[2 * k], f[2 * k + 1]);
           }
         }
         if (rope) {
@@ -129,7 +137,7 @@ rmsnorm_rope_pack_kernel(const uint16_t* __restrict__ x, int64_t s, int64_t D, i
         }
         V8 o;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o.v[j] = from_f<BF16>(f[j]);
+        for (int k = 0; k < 4; ++k) o.w[k] = pack2_rn<BF16>(f[2 * k], f[2 * k + 1]);
         *reinterpret_cast<V8*>(out + out_off[i] + t * ldo) = o;
       }
     }
