@@ -13,6 +13,7 @@
 #include <type_traits>
 
 #include "attn_common.cuh"
+#include "quant_common.cuh"
 
 namespace dax {
 namespace {
@@ -40,17 +41,24 @@ colstats_kernel(const uint16_t* __restrict__ k, const uint16_t* __restrict__ v, 
   const uint16_t* kb = k + b * ks.b + h * ks.h + cg * 8;
   const uint16_t* vb = v + b * vs.b + h * vs.h + cg * 8;
   float sum[8], mx[8];
+  uint32_t mx2[4] = {0u, 0u, 0u, 0u};  // packed running maxima of |V|
 #pragma unroll
-  for (int j = 0; j < 8; ++j) { sum[j] = 0.f; mx[j] = 0.f; }
+  for (int j = 0; j < 8; ++j) sum[j] = 0.f;
   for (int64_t t = t0 + tl; t < t1; t += 16) {
-    const V8 kv = *reinterpret_cast<const V8*>(kb + t * ks.t);
-    const V8 vv = *reinterpret_cast<const V8*>(vb + t * vs.t);
+    const uint4 kv = *reinterpret_cast<const uint4*>(kb + t * ks.t);
+    const uint4 vv = *reinterpret_cast<const uint4*>(vb + t * vs.t);
+    const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w}, vw[4] = {vv.x, vv.y, vv.z, vv.w};
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      sum[j] += ld16<BF16>(kv.v[j]);
-      mx[j] = fmaxf(mx[j], fabsf(ld16<BF16>(vv.v[j])));
+    for (int q = 0; q < 4; ++q) {
+      float lo, hi;
+      unpack2<BF16>(kw[q], lo, hi);
+      sum[2 * q] += lo;
+      sum[2 * q + 1] += hi;
+      mx2[q] = absmax2<BF16>(mx2[q], vw[q]);
     }
   }
+#pragma unroll
+  for (int q = 0; q < 4; ++q) unpack2<BF16>(mx2[q], mx[2 * q], mx[2 * q + 1]);
 #pragma unroll
   for (int j = 0; j < 8; ++j) { red[0][tl][cg * 8 + j] = sum[j]; red[1][tl][cg * 8 + j] = mx[j]; }
   __syncthreads();
@@ -78,78 +86,92 @@ __global__ void colstats_fin_kernel(const float* __restrict__ part, int64_t chun
   v_scale[bh * 128 + c] = fp8_v ? fmaxf(m / 448.f, 1e-30f) : 1.f;
 }
 
-// grid (Sq_pad / 8, BH), 256 threads: one warp per token, a lane owns 4 channels.
+// grid (Sq_pad / 64, BH), 256 threads: a warp owns 8 consecutive tokens, a lane 4 channels of each.  All eight
+// loads of a lane are issued before the first token is reduced.
 template <bool BF16, bool I8>
 __global__ void __launch_bounds__(256)
 quant_q_kernel(const uint16_t* __restrict__ q, Strides qs, int heads, int64_t Sq, int64_t Sq_pad, float cscale,
                void* __restrict__ qo, float* __restrict__ q_scale) {
+  constexpr int TPW = 8;  // tokens per warp
   const int bh = blockIdx.y, b = bh / heads, h = bh % heads;
   const int lane = threadIdx.x & 31;
-  const int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-  if (t >= Sq_pad) return;
-  float f[4] = {0.f, 0.f, 0.f, 0.f};
-  if (t < Sq) {
-    const uint2 raw = *reinterpret_cast<const uint2*>(q + b * qs.b + h * qs.h + t * qs.t + lane * 4);
-    f[0] = ld16<BF16>(raw.x & 0xffff); f[1] = ld16<BF16>(raw.x >> 16);
-    f[2] = ld16<BF16>(raw.y & 0xffff); f[3] = ld16<BF16>(raw.y >> 16);
-  }
-  const int64_t row = static_cast<int64_t>(bh) * Sq_pad + t;
-  if constexpr (I8) {
-    float amax = 0.f;
+  const int64_t t0 = static_cast<int64_t>(blockIdx.x) * 64 + (threadIdx.x >> 5) * TPW;
+  const uint16_t* src = q + b * qs.b + h * qs.h + lane * 4;
+  uint2 raw[TPW];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) { f[j] *= cscale; amax = fmaxf(amax, fabsf(f[j])); }
+  for (int i = 0; i < TPW; ++i)
+    raw[i] = t0 + i < Sq ? *reinterpret_cast<const uint2*>(src + (t0 + i) * qs.t) : make_uint2(0u, 0u);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    const float sc = fmaxf(amax / 127.f, 1e-30f);
-    const float inv = 1.f / sc;
-    uint32_t w = 0;
+  for (int i = 0; i < TPW; ++i) {
+    const int64_t t = t0 + i;
+    if (t >= Sq_pad) break;
+    float f[4];
+    unpack2<BF16>(raw[i].x, f[0], f[1]);
+    unpack2<BF16>(raw[i].y, f[2], f[3]);
+    const int64_t row = static_cast<int64_t>(bh) * Sq_pad + t;
+    if constexpr (I8) {
+      float amax = 0.f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int qi = max(-127, min(127, __float2int_rn(f[j] * inv)));
-      w |= (static_cast<uint32_t>(qi) & 0xffu) << (8 * j);
+      for (int j = 0; j < 4; ++j) { f[j] *= cscale; amax = fmaxf(amax, fabsf(f[j])); }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      const float sc = fmaxf(amax / 127.f, 1e-30f);
+      const float inv = 1.f / sc;
+      uint32_t w = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int qi = max(-127, min(127, __float2int_rn(f[j] * inv)));
+        w |= (static_cast<uint32_t>(qi) & 0xffu) << (8 * j);
+      }
+      reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(qo) + row * 128)[lane] = w;
+      if (lane == 0) q_scale[row] = sc;
+    } else {
+      // 16-bit scores: Q goes through unscaled, as bf16 (the scale is applied to the scores)
+      uint2 w;
+      w.x = pack2_rn<true>(f[0], f[1]);
+      w.y = pack2_rn<true>(f[2], f[3]);
+      reinterpret_cast<uint2*>(static_cast<uint16_t*>(qo) + row * 128)[lane] = w;
+      if (lane == 0) q_scale[row] = cscale;
     }
-    reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(qo) + row * 128)[lane] = w;
-    if (lane == 0) q_scale[row] = sc;
-  } else {
-    uint2 w;
-    w.x = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(f[0]))) | (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(f[1]))) << 16);
-    w.y = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(f[2]))) | (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(f[3]))) << 16);
-    reinterpret_cast<uint2*>(static_cast<uint16_t*>(qo) + row * 128)[lane] = w;
-    if (lane == 0) q_scale[row] = cscale;
   }
 }
 
-// grid (Sk_pad / 128, BH), 256 threads: thread = (token = tid / 2, half row of 64 channels).
+// grid (Sk_pad / 128, BH), 256 threads: thread = (8 channels, tokens tl, tl + 16, ..., tl + 112), so that a
+// warp's 16-byte loads cover two whole 256-byte token rows.
 template <bool BF16, bool I8>
 __global__ void __launch_bounds__(256)
 quant_k_kernel(const uint16_t* __restrict__ k, Strides ks, int heads, int64_t Sk, int64_t Sk_pad,
                const float* __restrict__ k_mean, void* __restrict__ ko, float* __restrict__ k_scale) {
   __shared__ float red[8];
-  __shared__ float mean_s[128];
   const int bh = blockIdx.y, b = bh / heads, h = bh % heads;
-  const int64_t t = static_cast<int64_t>(blockIdx.x) * 128 + (threadIdx.x >> 1);
-  const int c0 = (threadIdx.x & 1) * 64;
-  if (threadIdx.x < 128) mean_s[threadIdx.x] = k_mean[bh * 128 + threadIdx.x];
-  __syncthreads();
-  float f[64];
-  float amax = 0.f;
-  if (t < Sk) {
-    const uint16_t* src = k + b * ks.b + h * ks.h + t * ks.t + c0;
+  const int cg = threadIdx.x & 15, tl = threadIdx.x >> 4;
+  const int64_t tok0 = static_cast<int64_t>(blockIdx.x) * 128;
+  const uint16_t* src = k + b * ks.b + h * ks.h + cg * 8;
+  uint4 raw[8];
 #pragma unroll
-    for (int vi = 0; vi < 8; ++vi) {
-      const V8 raw = *reinterpret_cast<const V8*>(src + vi * 8);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float x = ld16<BF16>(raw.v[j]) - mean_s[c0 + vi * 8 + j];
-        f[vi * 8 + j] = x;
-        amax = fmaxf(amax, fabsf(x));
-      }
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 64; ++j) f[j] = 0.f;
+  for (int i = 0; i < 8; ++i) {
+    const int64_t t = tok0 + tl + 16 * i;
+    raw[i] = t < Sk ? *reinterpret_cast<const uint4*>(src + t * ks.t) : make_uint4(0u, 0u, 0u, 0u);
   }
-  const int64_t row = static_cast<int64_t>(bh) * Sk_pad + t;
+  float mean[8];
+  *reinterpret_cast<float4*>(&mean[0]) = *reinterpret_cast<const float4*>(k_mean + bh * 128 + cg * 8);
+  *reinterpret_cast<float4*>(&mean[4]) = *reinterpret_cast<const float4*>(k_mean + bh * 128 + cg * 8 + 4);
+  float f[8][8];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const bool live = tok0 + tl + 16 * i < Sk;
+    const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float lo, hi;
+      unpack2<BF16>(w[q], lo, hi);
+      f[i][2 * q] = live ? lo - mean[2 * q] : 0.f;
+      f[i][2 * q + 1] = live ? hi - mean[2 * q + 1] : 0.f;
+      amax = fmaxf(amax, fmaxf(fabsf(f[i][2 * q]), fabsf(f[i][2 * q + 1])));
+    }
+  }
+  const int64_t row0 = static_cast<int64_t>(bh) * Sk_pad + tok0 + tl;
   if constexpr (I8) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -160,64 +182,84 @@ quant_k_kernel(const uint16_t* __restrict__ k, Strides ks, int heads, int64_t Sk
     for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
     const float sc = fmaxf(amax / 127.f, 1e-30f);
     const float inv = 1.f / sc;
-    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(ko) + row * 128 + c0);
 #pragma unroll
-    for (int vi = 0; vi < 4; ++vi) {
-      uint32_t w[4];
+    for (int i = 0; i < 8; ++i) {
+      uint32_t w[2];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
+      for (int q = 0; q < 2; ++q) {
         w[q] = 0;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const int qi = max(-127, min(127, __float2int_rn(f[vi * 16 + q * 4 + j] * inv)));
+          const int qi = max(-127, min(127, __float2int_rn(f[i][q * 4 + j] * inv)));
           w[q] |= (static_cast<uint32_t>(qi) & 0xffu) << (8 * j);
         }
       }
-      dst[vi] = make_uint4(w[0], w[1], w[2], w[3]);
+      *reinterpret_cast<uint2*>(static_cast<uint8_t*>(ko) + (row0 + 16 * i) * 128 + cg * 8) = make_uint2(w[0], w[1]);
     }
     if (threadIdx.x == 0) k_scale[static_cast<int64_t>(bh) * (Sk_pad / 128) + blockIdx.x] = sc;
   } else {
-    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(ko) + row * 128 + c0);
 #pragma unroll
-    for (int vi = 0; vi < 8; ++vi) {
-      uint32_t w[4];
-#pragma unroll
-      for (int q = 0; q < 4; ++q)
-        w[q] = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(f[vi * 8 + 2 * q]))) |
-               (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(f[vi * 8 + 2 * q + 1]))) << 16);
-      dst[vi] = make_uint4(w[0], w[1], w[2], w[3]);
+    for (int i = 0; i < 8; ++i) {
+      uint4 w;
+      w.x = pack2_rn<true>(f[i][0], f[i][1]);
+      w.y = pack2_rn<true>(f[i][2], f[i][3]);
+      w.z = pack2_rn<true>(f[i][4], f[i][5]);
+      w.w = pack2_rn<true>(f[i][6], f[i][7]);
+      *reinterpret_cast<uint4*>(static_cast<uint16_t*>(ko) + (row0 + 16 * i) * 128 + cg * 8) = w;
     }
     if (threadIdx.x == 0) k_scale[static_cast<int64_t>(bh) * (Sk_pad / 128) + blockIdx.x] = 1.f;
   }
 }
 
 // grid (Sk_pad / 128, BH), 256 threads.  Reads a [128 tokens x 128 channels] tile row-wise, writes it
-// transposed: vt[bh, channel, token].  The transpose goes through shared memory with a padded pitch.
+// transposed: vt[bh, channel, token].  Thread = (8 channels, 8 consecutive tokens): it converts its 8 x 8 block,
+// gathers the 8 tokens of each channel into one 8- or 16-byte shared-memory store, and the warps then copy whole
+// channel rows out.
 template <bool BF16, bool F8>
 __global__ void __launch_bounds__(256)
 quant_v_kernel(const uint16_t* __restrict__ v, Strides vs, int heads, int64_t Sk, int64_t Sk_pad,
                const float* __restrict__ v_scale, void* __restrict__ vo) {
   using OutT = typename std::conditional<F8, uint8_t, uint16_t>::type;
-  constexpr int PITCH = 128 + (F8 ? 4 : 2);  // elements; keeps 4-byte alignment and spreads banks
-  __shared__ OutT tile[128 * PITCH];         // [channel][token]
-  __shared__ float inv_s[128];
+  constexpr int PITCH = 128 + 16 / static_cast<int>(sizeof(OutT));  // elements: rows 16 bytes apart in the banks
+  __shared__ __align__(16) OutT tile[128 * PITCH];                  // [channel][token]
   const int bh = blockIdx.y, b = bh / heads, h = bh % heads;
   const int64_t tok0 = static_cast<int64_t>(blockIdx.x) * 128;
-  if (threadIdx.x < 128) inv_s[threadIdx.x] = 1.f / v_scale[bh * 128 + threadIdx.x];
-  __syncthreads();
-  {
-    const int cg = threadIdx.x & 15;  // 8 channels
-    for (int tl = threadIdx.x >> 4; tl < 128; tl += 16) {
-      const int64_t t = tok0 + tl;
-      V8 raw;
-      if (t < Sk) raw = *reinterpret_cast<const V8*>(v + b * vs.b + h * vs.h + t * vs.t + cg * 8);
+  const int cg = threadIdx.x & 15, tq = threadIdx.x >> 4;
+  const uint16_t* src = v + b * vs.b + h * vs.h + cg * 8;
+  uint4 raw[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int c = cg * 8 + j;
-        const float x = t < Sk ? ld16<BF16>(raw.v[j]) * inv_s[c] : 0.f;
-        if constexpr (F8) tile[c * PITCH + tl] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
-        else tile[c * PITCH + tl] = __bfloat16_as_ushort(__float2bfloat16_rn(x));
-      }
+  for (int i = 0; i < 8; ++i) {
+    const int64_t t = tok0 + tq * 8 + i;
+    raw[i] = t < Sk ? *reinterpret_cast<const uint4*>(src + t * vs.t) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  float inv[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) inv[j] = 1.f / v_scale[bh * 128 + cg * 8 + j];
+  float x[8][8];  // [token][channel]
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float lo, hi;
+      unpack2<BF16>(w[q], lo, hi);
+      x[i][2 * q] = lo * inv[2 * q];
+      x[i][2 * q + 1] = hi * inv[2 * q + 1];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    OutT* dst = &tile[(cg * 8 + j) * PITCH + tq * 8];
+    if constexpr (F8) {
+      uint16_t p[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(p[i]) : "f"(x[2 * i + 1][j]), "f"(x[2 * i][j]));
+      *reinterpret_cast<uint2*>(dst) = make_uint2(static_cast<uint32_t>(p[0]) | (static_cast<uint32_t>(p[1]) << 16),
+                                                  static_cast<uint32_t>(p[2]) | (static_cast<uint32_t>(p[3]) << 16));
+    } else {
+      *reinterpret_cast<uint4*>(dst) = make_uint4(pack2_rn<true>(x[0][j], x[1][j]), pack2_rn<true>(x[2][j], x[3][j]),
+                                                  pack2_rn<true>(x[4][j], x[5][j]), pack2_rn<true>(x[6][j], x[7][j]));
     }
   }
   __syncthreads();
@@ -229,8 +271,7 @@ quant_v_kernel(const uint16_t* __restrict__ v, Strides vs, int heads, int64_t Sk
       if constexpr (F8) {
         reinterpret_cast<uint32_t*>(dst)[lane] = *reinterpret_cast<const uint32_t*>(&tile[c * PITCH + lane * 4]);
       } else {
-        reinterpret_cast<uint32_t*>(dst)[lane] = *reinterpret_cast<const uint32_t*>(&tile[c * PITCH + lane * 2]);
-        reinterpret_cast<uint32_t*>(dst)[32 + lane] = *reinterpret_cast<const uint32_t*>(&tile[c * PITCH + 64 + lane * 2]);
+        reinterpret_cast<uint2*>(dst)[lane] = *reinterpret_cast<const uint2*>(&tile[c * PITCH + lane * 4]);
       }
     }
   }
@@ -248,7 +289,7 @@ int run_prepare(const void* q, const void* k, const void* v, int64_t B, int64_t 
   const unsigned bh = static_cast<unsigned>(BH);
   colstats_kernel<BF16><<<dim3(static_cast<unsigned>(ws.chunks), bh), 256, 0, st>>>(kp, vp, ks, vs, static_cast<int>(heads), Sk, ws.part, ws.chunks);
   colstats_fin_kernel<<<bh, 128, 0, st>>>(ws.part, ws.chunks, Sk, v_f8 ? 1 : 0, ws.k_mean, ws.v_scale);
-  const dim3 gq(static_cast<unsigned>(ws.Sq_pad / 8), bh), gk(static_cast<unsigned>(ws.Sk_pad / 128), bh);
+  const dim3 gq(static_cast<unsigned>((ws.Sq_pad + 63) / 64), bh), gk(static_cast<unsigned>(ws.Sk_pad / 128), bh);
   if (qk_i8) {
     quant_q_kernel<BF16, true><<<gq, 256, 0, st>>>(qp, qs, static_cast<int>(heads), Sq, ws.Sq_pad, cscale, ws.q, ws.q_scale);
     quant_k_kernel<BF16, true><<<gk, 256, 0, st>>>(kp, ks, static_cast<int>(heads), Sk, ws.Sk_pad, ws.k_mean, ws.k, ws.k_scale);
