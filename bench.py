@@ -166,6 +166,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="dax_b200", choices=["dax_b200", "reference"])
     ap.add_argument("--workload", default="dit", choices=["dit", "hotpath"])
+    ap.add_argument("--loop", type=int, default=0,
+                    help="dit workload only: after the timed steps, also run one flow-matching loop of this many "
+                         "denoising steps (classifier-free guidance 5.0, TeaCache threshold 0.2) and report it")
     ap.add_argument("--layers", type=int, default=LAYERS, help=argparse.SUPPRESS)  # profiling captures only
     ap.add_argument("--tokens", type=int, default=TOKENS, help=argparse.SUPPRESS)  # profiling captures only
     ap.add_argument("--no-cpu-baseline", action="store_true", help=argparse.SUPPRESS)
@@ -296,6 +299,34 @@ def main():
     assert status == 0, f"device status {status}: a kernel wait timed out"
     assert torch.isfinite(y_host.float()).all(), "non-finite output"
 
+    # ---- optional: BASELINE config 5's loop (50 steps, guidance => two forwards per step, TeaCache 0.2) ----
+    loop = None
+    if dit and args.loop > 0:
+        from dax_b200.adapters.wan.sampling import denoise
+        from dax_b200.cache import teacache
+        teacache.configure(pipe.transformer, teacache_thresh=0.2, num_inference_steps=args.loop)
+        neg = torch.randn(1, TEXT_TOKENS, TEXT_DIM, generator=gx).to(torch.bfloat16).to(dev)
+        computed = [0]
+
+        def count(i, _x):
+            computed[0] += int(bool(pipe.transformer.should_calc_even)) + int(bool(pipe.transformer.should_calc_odd))
+
+        barrier()
+        e0.record()
+        out = denoise(pipe, x_dev, text, neg, num_inference_steps=args.loop, guidance_scale=5.0, flow_shift=5.0,
+                      on_step=count)
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if sp:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        pipe.transformer.__class__.enable_teacache = False
+        assert torch.isfinite(out.float()).all(), "non-finite sample"
+        loop = {"denoising_steps": args.loop, "forwards": 2 * args.loop, "forwards_computed": computed[0],
+                "forwards_skipped": 2 * args.loop - computed[0], "ms_total": float(t.item()),
+                "ms_per_denoising_step": float(t.item()) / args.loop, "guidance_scale": 5.0, "teacache_thresh": 0.2,
+                "solver": "first-order flow matching (Euler), flow_shift 5.0"}
+
     if rank != 0:
         if sp:
             dist.barrier()
@@ -340,6 +371,8 @@ def main():
             "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
             "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
             "kernel_ms_per_step": breakdown}
+    if loop is not None:
+        line["denoise_loop"] = loop
     print(json.dumps(line), flush=True)
     if sp:
         dist.barrier()

@@ -175,3 +175,34 @@ def test_dit_forward_and_teacache(ops):
     assert m.should_calc_even is False and m.should_calc_odd is False
     assert O.rel_l2(outs[2].float().cpu(), outs[0].float().cpu()) <= 1e-2
     cls.enable_teacache = False
+
+
+def test_denoise_loop_with_teacache(ops):
+    """Ten guided denoising steps of a small DiT through the optimised forward: the cache must skip some of the
+    twenty forwards, never during the first ten calls, and the sample must stay finite and close to the one
+    computed without the cache."""
+    from dax_b200.adapters.wan import optimize_pipe
+    from dax_b200.adapters.wan.modules import _Pipe
+    from dax_b200.adapters.wan.sampling import denoise
+    from dax_b200.cache import teacache
+    m = build_dit(layers=2, seed=11).to(DEV)
+    pipe = _Pipe(m)
+    optimize_pipe(pipe, sequence_parallel=False, compile=False, overlap_comm=False, int8_linear=True,
+                  attention_mode="bf16")
+    g = torch.Generator().manual_seed(5)
+    lat = torch.randn(1, 16, 2, 16, 16, generator=g).bfloat16().to(DEV)
+    pos = torch.randn(1, 11, 64, generator=g).bfloat16().to(DEV)
+    neg = torch.randn(1, 11, 64, generator=g).bfloat16().to(DEV)
+    plain = denoise(pipe, lat, pos, neg, num_inference_steps=10, guidance_scale=3.0, flow_shift=3.0)
+    teacache.configure(m, teacache_thresh=0.05, num_inference_steps=10)
+    calc = []
+    cached = denoise(pipe, lat, pos, neg, num_inference_steps=10, guidance_scale=3.0, flow_shift=3.0,
+                     on_step=lambda i, x: calc.append((bool(m.should_calc_even), bool(m.should_calc_odd))))
+    type(m).enable_teacache = False
+    assert m.cnt == 20 and len(calc) == 10
+    assert all(c == (True, True) for c in calc[:5])      # ret_steps = 10 forwards
+    assert torch.isfinite(cached.float()).all() and torch.isfinite(plain.float()).all()
+    if any(c != (True, True) for c in calc):             # skipped forwards reuse a residual: close, not equal
+        assert O.rel_l2(cached.float().cpu(), plain.float().cpu()) <= 0.2
+    else:
+        assert torch.equal(cached, plain)

@@ -57,3 +57,54 @@ def test_temb_variant_windows():
     t = T()
     teacache.configure(t, teacache_thresh=0.1, num_inference_steps=50, use_ref_steps=False)
     assert t.ret_steps == 2 and t.cutoff_steps == 98 and len(t.coefficients) == 5
+
+
+# ---- the denoising loop that drives the cached forward (dax_b200/adapters/wan/sampling.py) ----------------
+def test_flow_match_sigmas():
+    from dax_b200.adapters.wan.sampling import flow_match_sigmas
+    s = flow_match_sigmas(50, flow_shift=5.0)
+    assert s.shape == (51,) and float(s[0]) == 1.0 and float(s[-1]) == 0.0
+    assert torch.all(s[1:] < s[:-1])
+    # the shift keeps more steps at high noise: the midpoint of the schedule sits well above 0.5
+    assert float(s[25]) > 0.8
+    plain = flow_match_sigmas(50, flow_shift=1.0)
+    assert abs(float(plain[25]) - (1.0 - 25 * (1.0 - 1e-3) / 49)) < 1e-6
+
+
+def test_denoise_loop_integrates_and_drives_the_cache():
+    from dax_b200.adapters.wan.sampling import denoise
+
+    class Stub(torch.nn.Module):
+        """velocity = c for the prompt, c / 2 for the negative prompt; counts its calls like the cached DiT"""
+        def __init__(self):
+            super().__init__()
+            self.calls = []
+
+        def forward(self, x, t, ctx, return_dict=False):
+            self.calls.append((float(t[0]), float(ctx.flatten()[0])))
+            self.cnt += 1
+            return (torch.full_like(x, 2.0 * float(ctx.flatten()[0])),)
+
+    class Pipe:
+        pass
+
+    pipe = Pipe()
+    pipe.transformer = Stub()
+    pipe.transformer.cnt = 7  # stale counter of an earlier trajectory: the loop must reset it
+    x0 = torch.zeros(1, 2, 1, 4, 4)
+    pos, neg = torch.ones(1, 3, 8), torch.full((1, 3, 8), 0.5)
+    seen = []
+    out = denoise(pipe, x0, pos, neg, num_inference_steps=10, guidance_scale=5.0, flow_shift=3.0,
+                  on_step=lambda i, x: seen.append(i))
+    # v = v_u + g (v_c - v_u) = 1 + 5 * (2 - 1) = 6, integrated from sigma = 1 to 0: x = x0 - 6
+    assert torch.allclose(out, torch.full_like(x0, -6.0), atol=1e-5)
+    assert seen == list(range(10)) and pipe.transformer.cnt == 20
+    # conditional first, then unconditional, at the same timestep; timesteps run from 1000 downwards
+    assert [c[1] for c in pipe.transformer.calls[:4]] == [1.0, 0.5, 1.0, 0.5]
+    assert pipe.transformer.calls[0][0] == 1000.0 and pipe.transformer.calls[0][0] == pipe.transformer.calls[1][0]
+    ts = [c[0] for c in pipe.transformer.calls[::2]]
+    assert all(a > b for a, b in zip(ts, ts[1:]))
+    # without guidance: one forward per step
+    pipe.transformer.calls.clear()
+    denoise(pipe, x0, pos, None, num_inference_steps=4)
+    assert len(pipe.transformer.calls) == 4
