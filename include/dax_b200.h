@@ -180,7 +180,7 @@ int dax_rmsnorm_rope_pack(const void* x, int dtype, int64_t s, int64_t D, int64_
 /* ---------------------------------------------------------------------------------------------
  * LayerNorm + adaLN modulation (+ per-token quantisation): the step in front of every quantised linear
  * of a Wan DiT block outside the attention itself (the block is diffusers code called from
- * dax/adapters/wan/transformer_adapter.py:130-136; the quantiser it absorbs is
+ * dax/adapters/wan/transformer_adapter.py:127-134; the quantiser it absorbs is
  * dax/quant/nn/dynamic/functional.py:54-148).
  *   y = round_dtype( LN(x; eps) [* ln_weight + ln_bias] [* (1 + scale) + shift] )      per token row
  *   (q, qscale) = per-token dynamic quantisation of y (bit-exact with dax_quant_rowwise applied to y)
