@@ -220,7 +220,12 @@ class WanDiT(nn.Module):
     def rope(self, hidden_states: torch.Tensor) -> torch.Tensor:
         _, _, f, h, w = hidden_states.shape
         pt, ph, pw = self.config.patch_size
-        return wan_rope_table((f // pt, h // ph, w // pw), self.config.attention_head_dim, device=hidden_states.device)
+        key = ((f // pt, h // ph, w // pw), str(hidden_states.device))
+        cache = self.__dict__.setdefault("_rope_cache", {})
+        if key not in cache:  # the table depends on the token grid only: build and upload it once
+            cache.clear()
+            cache[key] = wan_rope_table(key[0], self.config.attention_head_dim, device=hidden_states.device)
+        return cache[key]
 
     def unpatchify(self, x: torch.Tensor, batch: int, grid) -> torch.Tensor:
         pt, ph, pw = self.config.patch_size
