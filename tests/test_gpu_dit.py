@@ -45,6 +45,24 @@ def test_layernorm_modulate_quant(ops, dtype, D):
             assert torch.equal(q3, q) and torch.equal(qs3, qs)
 
 
+def test_layernorm_modulate_quant_many_rows(ops):
+    """More rows than resident CTAs at the production width: the row loop with prefetch, against the oracle and
+    against the same rows processed one at a time."""
+    torch.manual_seed(9)
+    s, D = 2000, 5120
+    x = (torch.randn(s, D) * torch.logspace(-1, 1.5, s).unsqueeze(1) + 0.3).bfloat16()
+    shift, scale = 0.2 * torch.randn(D), 0.2 * torch.randn(D)
+    ref = (O.layernorm(x) * (1 + scale) + shift).bfloat16()
+    y, q, qs = ops.layernorm_modulate_quant(x.to(DEV), shift=shift.to(DEV), scale=scale.to(DEV), q_dtype=torch.float8_e4m3fn)
+    assert O.rel_l2(y.cpu(), ref) <= 3e-3
+    qr, sr = O.quantize_rowwise(y.cpu(), torch.float8_e4m3fn)
+    assert torch.equal(q.cpu().view(torch.uint8), qr.view(torch.uint8)) and torch.equal(qs.cpu(), sr)
+    for i in (0, 1, 295, 296, 443, 444, 1999):
+        yi, qi, si = ops.layernorm_modulate_quant(x[i:i + 1].to(DEV), shift=shift.to(DEV), scale=scale.to(DEV),
+                                                  q_dtype=torch.float8_e4m3fn)
+        assert torch.equal(yi[0], y[i]) and torch.equal(qi[0], q[i]) and torch.equal(si[0], qs[i])
+
+
 @pytest.mark.parametrize("wdt", [torch.int8, torch.float8_e4m3fn])
 def test_gemm_epilogues(ops, wdt):
     torch.manual_seed(3)

@@ -65,6 +65,14 @@ def test_quantiser_grouped_columns_and_empty(ops):
     q, s = ops.quant_rowwise(slabs.to(DEV), torch.int8, col_group=hd, group_stride=n * hd, rows=n, cols=P * hd, ldx=hd)
     qr, sr = O.quantize_rowwise(mat, torch.int8)
     assert torch.equal(q.cpu(), qr) and torch.equal(s.cpu(), sr)
+    # the same through the row-pipelined kernel (rows of more than 256 vectors): 8 slabs of 640 columns, FP8 and INT8
+    P, n, hd = 8, 301, 640
+    slabs = torch.randn(P, n, hd).bfloat16()
+    mat = slabs.permute(1, 0, 2).reshape(n, P * hd).contiguous()
+    for qd in (torch.int8, torch.float8_e4m3fn):
+        q, s = ops.quant_rowwise(slabs.to(DEV), qd, col_group=hd, group_stride=n * hd, rows=n, cols=P * hd, ldx=hd)
+        qr, sr = O.quantize_rowwise(mat, qd)
+        assert torch.equal(bits(q.cpu()), bits(qr)) and torch.equal(s.cpu(), sr)
     q, s = ops.quant_rowwise(torch.empty(0, 64, device=DEV).bfloat16(), torch.int8)
     assert q.shape == (0, 64)
     with pytest.raises(ValueError):
@@ -202,6 +210,33 @@ def test_gemm_full_size_linearity(ops):
 
 
 # ---- RMSNorm + RoPE + pack ---------------------------------------------------------------------------
+def test_rmsnorm_rope_pack_many_rows_full_width(ops):
+    """Production width (5120 = 40 heads, three vectors per thread, the third ragged) and more rows than resident
+    CTAs, so that every CTA strides over several rows with the next row's loads in flight."""
+    torch.manual_seed(5)
+    grid = (3, 20, 25)
+    S, H = 1500, 40
+    D = H * 128
+    x = (torch.randn(S, D) * torch.logspace(-1, 1, S).unsqueeze(1)).bfloat16()
+    w = (1 + 0.1 * torch.randn(D)).bfloat16()
+    fr = O.rope_table(grid)
+    ref = O.rmsnorm(x.unsqueeze(0), w).unflatten(2, (H, -1)).transpose(1, 2)
+    ref = O.apply_rotary_emb(ref, fr).transpose(1, 2).flatten(2, 3)[0]
+    cos = fr.real.float().reshape(S, 64).contiguous().to(DEV)
+    sin = fr.imag.float().reshape(S, 64).contiguous().to(DEV)
+    y = ops.rmsnorm_rope_pack(x.to(DEV), norm_weight=w.to(DEV), do_norm=True, rope_cos=cos, rope_sin=sin)
+    assert O.rel_l2(y.cpu(), ref) <= 2e-3
+    parts = x.float().pow(2).view(S, D // 128, 128).sum(-1).to(DEV)   # 40 partials per row, as the GEMM writes them
+    y2 = ops.rmsnorm_rope_pack(x.to(DEV), norm_weight=w.to(DEV), do_norm=True, rope_cos=cos, rope_sin=sin, row_sumsq=parts)
+    assert O.rel_l2(y2.cpu(), ref) <= 2e-3
+    # every row on its own equals the row inside the batch (no cross-row leakage through the prefetch registers)
+    idx = torch.tensor([0, 1, 443, 444, 445, 887, 1499])
+    for i in idx.tolist():
+        yi = ops.rmsnorm_rope_pack(x[i:i + 1].to(DEV), norm_weight=w.to(DEV), do_norm=True, rope_cos=cos, rope_sin=sin,
+                                   token_offset=i)
+        assert torch.equal(yi[0], y[i])
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_rmsnorm_rope_pack(ops, dtype):
     torch.manual_seed(3)
