@@ -166,6 +166,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="dax_b200", choices=["dax_b200", "reference"])
     ap.add_argument("--workload", default="dit", choices=["dit", "hotpath"])
+    ap.add_argument("--qkv-chunks", type=int, default=0,
+                    help="sequence parallel only: row chunks of the Q/K/V projections whose exchange overlaps the "
+                         "next chunk (0 = the processor's default)")
     ap.add_argument("--loop", type=int, default=0,
                     help="dit workload only: after the timed steps, also run one flow-matching loop of this many "
                          "denoising steps (classifier-free guidance 5.0, TeaCache threshold 0.2) and report it")
@@ -222,6 +225,11 @@ def main():
     pipe = _Pipe(model)
     optimize_pipe(pipe, sequence_parallel=sp, compile=False, overlap_comm=sp, fp8_linear=True,
                   attention_mode=args.attention_mode)
+    if args.qkv_chunks > 0:
+        for mod in model.modules():
+            proc = getattr(mod, "processor", None)
+            if proc is not None and hasattr(proc, "qkv_chunks"):
+                proc.qkv_chunks = args.qkv_chunks
     torch.cuda.empty_cache()
 
     gx = torch.Generator().manual_seed(99)
