@@ -32,10 +32,6 @@ SIGNATURES = {
                                     c_int, c_void_p, c_int64, c_void_p, c_void_p]),
     "dax_layernorm_modulate_quant": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
                                              c_void_p, c_float, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p]),
-    "dax_gemm_i8_dequant": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                                    c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
-    "dax_gemm_f8_dequant": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                                    c_int, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "dax_linear_dynamic_workspace_bytes": (c_size_t, [c_int64, c_int64]),
     "dax_linear_dynamic": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                    c_int, c_void_p, c_int, c_int64, c_int64, c_void_p, c_size_t, c_void_p]),

@@ -36,33 +36,7 @@
 namespace dax {
 namespace {
 
-#ifdef DAX_ATTN_PROFILE
-// Phase timing for kernel tuning: compiled only when the macro is given on the command line.
-__device__ unsigned long long g_attn_prof[16];
-#define PROF_DECL unsigned long long prof_t0 = clock64(), prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0}
-#define PROF_MARK(i) do { unsigned long long t_ = clock64(); prof_acc[i] += t_ - prof_t0; prof_t0 = t_; } while (0)
-#define PROF_FLUSH() do { if (blockIdx.x == 3 && blockIdx.y == 0 && warp == DAX_ATTN_PROFILE && lane == 0) { for (int i_ = 0; i_ < 10; ++i_) g_attn_prof[i_] = prof_acc[i_]; g_attn_prof[15] = n_kv; } } while (0)
-#else
-#define PROF_DECL
-#define PROF_MARK(i)
-#define PROF_FLUSH()
-#endif
-
-#ifdef DAX_ATTN_TRACE
-// Event timestamps of one CTA for a few KV iterations (kernel tuning only).
-__device__ unsigned long long g_attn_trace[20 * 8 * 12];
-#define TR(ev) do { if (blockIdx.x == 3 && blockIdx.y == 0 && lane == 0 && j >= 60 && j < 68) g_attn_trace[(warp * 8 + (j - 60)) * 12 + (ev)] = clock64(); } while (0)
-#else
-#define TR(ev)
-#endif
-
 constexpr int PRODUCER_WARP = 16;
-#ifndef DAX_ATTN_ISSUERS_8BIT
-#define DAX_ATTN_ISSUERS_8BIT 2
-#endif
-#ifndef DAX_ATTN_ISSUERS_16BIT
-#define DAX_ATTN_ISSUERS_16BIT 3
-#endif
 constexpr int SOFTMAX_WARPS = 16;
 constexpr int BOX_BYTES = 128 * 128;  // one [128 x 128 B] box
 
@@ -71,7 +45,7 @@ template <> struct AttnCfg<DAX_ATTN_QK_I8_PV_F8> {
   static constexpr int QK_KIND = KIND_I8, PV_KIND = KIND_F8;
   static constexpr int EQ = 1, EP = 1;       // bytes per element of Q/K and of P/V
   static constexpr int NSLOT = 8;            // 8 x 16 KB: four (K, V) pairs in flight
-  static constexpr int ISSUERS = DAX_ATTN_ISSUERS_8BIT;
+  static constexpr int ISSUERS = 2;
   static constexpr float TAU = 0.f;          // P is scaled to the e4m3 range: the row max must be exact
   static constexpr float PBIAS = 8.8073549f; // log2(448): P in (0, 448]
 };
@@ -79,7 +53,7 @@ template <> struct AttnCfg<DAX_ATTN_QK_BF16_PV_BF16> {
   static constexpr int QK_KIND = KIND_F16, PV_KIND = KIND_F16;
   static constexpr int EQ = 2, EP = 2;
   static constexpr int NSLOT = 2;            // 2 x 32 KB: shared memory is full (Q 64 KB + P 64 KB + ring 64 KB)
-  static constexpr int ISSUERS = DAX_ATTN_ISSUERS_16BIT;
+  static constexpr int ISSUERS = 3;
   static constexpr float TAU = 8.f;          // lazy rescale: P <= 2^8, far inside the bf16 range
   static constexpr float PBIAS = 0.f;
 };
@@ -87,7 +61,7 @@ template <> struct AttnCfg<DAX_ATTN_QK_I8_PV_BF16> {
   static constexpr int QK_KIND = KIND_I8, PV_KIND = KIND_F16;
   static constexpr int EQ = 1, EP = 2;
   static constexpr int NSLOT = 3;            // 3 x 32 KB (K tiles use half a slot): Q 32 KB + P 64 KB + ring 96 KB
-  static constexpr int ISSUERS = DAX_ATTN_ISSUERS_16BIT;
+  static constexpr int ISSUERS = 3;
   static constexpr float TAU = 8.f;
   static constexpr float PBIAS = 0.f;
 };
@@ -158,13 +132,9 @@ __device__ __forceinline__ uint32_t pack_bf16x2_trunc(float a, float b) {
   return r;
 }
 __device__ __forceinline__ float ex2(float x) {
-#ifdef DAX_ATTN_X_NOEXP  // tuning experiment only: take the exponential unit out of the picture
-  return x * 0.001f + 1.0f;
-#else
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-#endif
 }
 
 __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
@@ -233,17 +203,10 @@ __device__ __forceinline__ float exp_and_store64(const uint32_t (&sv)[64], float
 #pragma unroll
       for (int i = 0; i < 16; ++i) e[i] = pv(16 * c + i);
       uint4 w;
-#ifdef DAX_ATTN_X_NOCVT  // tuning experiment only (wrong results): no FP8 conversion
-      w.x = __float_as_uint(e[0] + e[1] + e[2] + e[3]);
-      w.y = __float_as_uint(e[4] + e[5] + e[6] + e[7]);
-      w.z = __float_as_uint(e[8] + e[9] + e[10] + e[11]);
-      w.w = __float_as_uint(e[12] + e[13] + e[14] + e[15]);
-#else
       w.x = pack_e4m3x4(e[0], e[1], e[2], e[3]);
       w.y = pack_e4m3x4(e[4], e[5], e[6], e[7]);
       w.z = pack_e4m3x4(e[8], e[9], e[10], e[11]);
       w.w = pack_e4m3x4(e[12], e[13], e[14], e[15]);
-#endif
       const int ck = 4 * half + c;
       *reinterpret_cast<uint4*>(p_tile + r * 128 + ((ck ^ (r & 7)) << 4)) = w;
     }
@@ -368,7 +331,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         {  // K_j : [128 tokens x 128 channels]
           const uint32_t s = seq % C::NSLOT, ph = (seq / C::NSLOT) & 1u;
           if (!mbar_wait(&kv_empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
-          TR(0);
           mbar_arrive_expect_tx(&kv_full[s], BOX_BYTES * C::EQ);
           for (int sub = 0; sub < C::EQ; ++sub)
             tma_load_2d(smem + L::OFF_RING + s * L::SLOT + sub * BOX_BYTES, &map_k, &kv_full[s], sub * 64,
@@ -378,7 +340,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         {  // V_j^T : [128 channels x 128 tokens]
           const uint32_t s = seq % C::NSLOT, ph = (seq / C::NSLOT) & 1u;
           if (!mbar_wait(&kv_empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
-          TR(1);
           mbar_arrive_expect_tx(&kv_full[s], BOX_BYTES * C::EP);
           for (int sub = 0; sub < C::EP; ++sub)
             tma_load_2d(smem + L::OFF_RING + s * L::SLOT + sub * BOX_BYTES, &map_v, &kv_full[s],
@@ -413,7 +374,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         // S_x(j-1) has been copied to registers by all eight warps of the tile
         if (j > 0 && !mbar_wait(&s_free[x], (j - 1) & 1u, abort_flag)) return false;
         tc_fence_after_sync();
-        TR(0);
         if constexpr (C::QK_KIND == KIND_I8) {
           // one bf16 K=16 instruction writes the float 12582912 into every accumulator; the integer
           // instructions then add the dot products to that bit pattern
@@ -422,7 +382,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         mma_tile<C::QK_KIND, C::EQ>(s_tm, q_addr + x * L::Q_TILE, ring + slot * L::SLOT, idesc_qk, C::QK_KIND == KIND_I8);
         umma_commit(&s_full[x]);
         umma_commit(&kv_empty[slot]);  // two arrivals free the slot: one per tile
-        TR(2);
         return true;
       };
       auto issue_pv = [&](int j, int x) -> bool {  // O_x += P_x . V_j
@@ -430,11 +389,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (!mbar_wait(&kv_full[slot], ph, abort_flag)) return false;
         if (!mbar_wait(&p_full[x], j & 1u, abort_flag)) return false;
         tc_fence_after_sync();
-        TR(1);
         mma_tile<C::PV_KIND, C::EP>(tmem_base + 256 + x * 128, p_addr + x * L::P_TILE, ring + slot * L::SLOT, idesc_pv, j > 0);
         umma_commit(&pv_done[x]);
         umma_commit(&kv_empty[slot]);  // the other tile's P.V supplies the second arrival
-        TR(3);
         return true;
       };
       if constexpr (C::ISSUERS == 2) {
@@ -467,16 +424,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     float m = -INFINITY, l = 0.f;
     float ks_next = ks[0];
     bool ok = true;
-    PROF_DECL;
 
     for (int j = 0; j < n_kv; ++j) {
       const float kscale = ks_next;
       if (j + 1 < n_kv) ks_next = ks[j + 1];
-      PROF_MARK(7);
       if (!mbar_wait(&s_full[x], j & 1u, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
-      PROF_MARK(0);
-      TR(0);
       uint32_t sv[64];
       tmem_ld32(s_tmem, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
       tmem_ld32(s_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
@@ -484,23 +437,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free[x]);  // S_X is in registers: Q.K^T of the next tile may start
-      PROF_MARK(1);
-      TR(1);
 
       const float cmul = sq * kscale;
       const int valid = p.Sk - j * 128 - half * 64;  // columns >= valid are padding (only in the last tile)
       if (valid < 64) mask_padding64(sv, valid);
       const float pm = row_max64<MODE>(sv, cmul);
-      TR(2);
-#ifdef DAX_ATTN_X_NOXCHG  // tuning experiment only (wrong results): no exchange with the partner thread
-      float pm2 = pm;
-#else
       xchg_write(slot(j & 1, half), pm, static_cast<uint32_t>(j + 1));
       float pm2;
       if (!xchg_read(slot(j & 1, half ^ 1), static_cast<uint32_t>(j + 1), pm2, abort_flag)) { ok = false; break; }
-#endif
-      PROF_MARK(2);
-      TR(3);
       const float mx = fmaxf(pm, pm2);
       const float m_new = (mx > m + C::TAU) ? mx : m;
       const float alpha = ex2(m - m_new);  // m = -inf on the first tile -> 0
@@ -510,15 +454,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (!mbar_wait(&pv_done[x], (j - 1) & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
       }
-      PROF_MARK(3);
-      TR(4);
-      PROF_MARK(8);
-      TR(5);
       const float sum = exp_and_store64<MODE>(sv, cmul, off, p_tile, r, half);
       l = fmaf(l, alpha, sum);
       m = m_new;
-      PROF_MARK(4);
-      TR(6);
 
       // correction: O_X *= alpha when any row of this warp moved its maximum (P_X . V_{j-1} is complete)
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
@@ -532,16 +470,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tmem_st32(o_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&ov[32]));
         tmem_wait_st();
       }
-      PROF_MARK(5);
-      TR(7);
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[x]);
-      PROF_MARK(6);
-      TR(8);
     }
-    PROF_FLUSH();
 
     if (ok && mbar_wait(&pv_done[x], (n_kv - 1) & 1u, abort_flag)) {
       tc_fence_after_sync();
@@ -628,11 +561,6 @@ int launch_fwd(const AttnWorkspace& ws, const AttnParams& p, int64_t BH, cudaStr
   return DAX_OK;
 }
 
-#ifdef DAX_ATTN_PROFILE
-}  // namespace
-unsigned long long (&prof_symbol())[16] { return g_attn_prof; }
-namespace {
-#endif
 }  // namespace
 }  // namespace dax
 
@@ -674,13 +602,3 @@ extern "C" int dax_attn_forward(void* o, int dtype, int64_t B, int64_t heads, in
   return launch_fwd<DAX_ATTN_QK_BF16_PV_BF16>(ws, p, B * heads, st);
 }
 
-#ifdef DAX_ATTN_TRACE
-extern "C" int dax_attn_trace_read(unsigned long long* host, int n) {
-  return cudaMemcpyFromSymbol(host, dax::g_attn_trace, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : 4;
-}
-#endif
-#ifdef DAX_ATTN_PROFILE
-extern "C" int dax_attn_profile_read(unsigned long long* host16) {
-  return cudaMemcpyFromSymbol(host16, dax::prof_symbol(), sizeof(unsigned long long) * 16) == cudaSuccess ? 0 : 4;
-}
-#endif

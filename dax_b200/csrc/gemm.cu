@@ -429,17 +429,3 @@ extern "C" int dax_gemm_dequant_ex(const void* qx, int a_dtype, const float* sx,
   const uint32_t idesc = make_idesc(/*c=f32*/ 1, a_dtype == DAX_E5M2 ? 1 : 0, b_dtype == DAX_E5M2 ? 1 : 0, BM, BN);
   return launch_gemm_out<KIND_F8>(out_dtype, map_a, map_b, p, idesc, grid, st);
 }
-
-extern "C" int dax_gemm_i8_dequant(const void* qx, const float* sx, const void* qw, const float* sw, const void* bias,
-                                   int bias_dtype, void* out, int out_dtype, int64_t M, int64_t N, int64_t K,
-                                   int64_t ldo, float* row_sumsq, int32_t* acc_dump, void* stream) {
-  return dax_gemm_dequant(qx, DAX_I8, sx, qw, DAX_I8, sw, bias, bias_dtype, out, out_dtype, M, N, K, ldo, N, 0,
-                          row_sumsq, acc_dump, stream);
-}
-
-extern "C" int dax_gemm_f8_dequant(const void* qx, int a_dtype, const float* sx, const void* qw, const float* sw,
-                                   const void* bias, int bias_dtype, void* out, int out_dtype, int64_t M, int64_t N,
-                                   int64_t K, int64_t ldo, float* row_sumsq, float* acc_dump, void* stream) {
-  return dax_gemm_dequant(qx, a_dtype, sx, qw, DAX_E4M3, sw, bias, bias_dtype, out, out_dtype, M, N, K, ldo, N, 0,
-                          row_sumsq, acc_dump, stream);
-}

@@ -110,14 +110,6 @@ int dax_gemm_dequant_ex(const void* qx, int a_dtype, const float* sx, const void
                         float* row_sumsq, void* acc_dump, int act, const void* resid, int64_t ldr,
                         const float* gate, void* stream);
 
-/* Same kernel under the two names a binding would look for. */
-int dax_gemm_i8_dequant(const void* qx, const float* sx, const void* qw, const float* sw, const void* bias,
-                        int bias_dtype, void* out, int out_dtype, int64_t M, int64_t N, int64_t K,
-                        int64_t ldo, float* row_sumsq, int32_t* acc_dump, void* stream);
-int dax_gemm_f8_dequant(const void* qx, int a_dtype, const float* sx, const void* qw, const float* sw,
-                        const void* bias, int bias_dtype, void* out, int out_dtype, int64_t M, int64_t N,
-                        int64_t K, int64_t ldo, float* row_sumsq, float* acc_dump, void* stream);
-
 /* ---------------------------------------------------------------------------------------------
  * One-call dynamic quantised linear = dax_quant_rowwise followed by dax_gemm_dequant, i.e. the whole of
  * dax.quant.nn.dynamic.Linear.forward (dax/quant/nn/dynamic/linear.py:143-228) for a plain row-major

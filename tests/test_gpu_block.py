@@ -1,5 +1,5 @@
 """The drop-in surface end to end on one GPU: module swap + attention processor against the oracle's
-restatement of the reference block (config 1 shape: 1024 tokens, hidden 1536, 12 heads)."""
+restatement of the reference block (the Wan2.1-1.3B-shaped layer: 1024 tokens, hidden 1536, 12 heads)."""
 import os
 
 import pytest

@@ -128,7 +128,7 @@ def test_sage_model_error_budget():
 
 
 def test_block_int8_linear_error_vs_float():
-    """Config 1 shape (1024 tokens, 1536 hidden, 12 heads): the quantised block stays within the
+    """Wan2.1-1.3B layer shape (1536 hidden, 12 heads): the quantised block stays within the
     quantisation error of the float block (sanity of the whole restatement)."""
     torch.manual_seed(0)
     S, D, H = 256, 1536, 12
