@@ -56,20 +56,25 @@ class _Buffers:
 
 
 _BUFFERS = _Buffers()
-_ROPE_CACHE: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
+_ROPE_CACHE: Dict[Tuple, Tuple[torch.Tensor, int, torch.Tensor, torch.Tensor]] = {}
 
 
 def _rope_tables(rotary_emb: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Complex ``[1, 1, S, 64]`` table -> fp32 cos / sin ``[S, 64]`` (cached per table)."""
+    """Complex ``[1, 1, S, 64]`` table -> fp32 cos / sin ``[S, 64]``, cached per table.
+
+    An entry keeps its source tensor alive, so the allocator cannot hand the same address to a later table
+    of the same shape with different content (pipelines build a fresh table every forward), and it records
+    the tensor's version counter, so an in-place update of the table is noticed too."""
     key = (rotary_emb.data_ptr(), tuple(rotary_emb.shape), str(rotary_emb.device), rotary_emb.dtype)
     hit = _ROPE_CACHE.get(key)
-    if hit is None:
-        if len(_ROPE_CACHE) > 8:
-            _ROPE_CACHE.clear()
-        r = torch.view_as_real(rotary_emb.reshape(-1, rotary_emb.shape[-1]))
-        hit = (r[..., 0].to(torch.float32).contiguous(), r[..., 1].to(torch.float32).contiguous())
-        _ROPE_CACHE[key] = hit
-    return hit
+    if hit is not None and hit[1] == rotary_emb._version:
+        return hit[2], hit[3]
+    if len(_ROPE_CACHE) >= 4:
+        _ROPE_CACHE.clear()
+    r = torch.view_as_real(rotary_emb.reshape(-1, rotary_emb.shape[-1]))
+    cos, sin = r[..., 0].to(torch.float32).contiguous(), r[..., 1].to(torch.float32).contiguous()
+    _ROPE_CACHE[key] = (rotary_emb, rotary_emb._version, cos, sin)
+    return cos, sin
 
 
 class DAXWanAttnProcessor2_0:

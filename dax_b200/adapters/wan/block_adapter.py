@@ -51,8 +51,11 @@ def fused_block_forward(self, hidden_states, encoder_hidden_states, temb, rotary
         h = p1._self_attention(self.attn1, y if y is not None else h, rotary_emb,
                                prequant=(q, qs) if q is not None else None, resid=h, gate=gate_msa)
         # 2. cross-attention over the text context: affine LN -> attention -> h + O(.)
-        y, q, qs = ops.layernorm_modulate_quant(h, eps=self.norm2.eps, ln_weight=w2, ln_bias=b2, q_dtype=q2,
-                                                want_y=q2 is None)
+        if isinstance(self.norm2, torch.nn.Identity):  # cross_attn_norm=False: no LayerNorm in front of attn2
+            y, (q, qs) = h, (ops.quant_rowwise(h, q2) if q2 is not None else (None, None))
+        else:
+            y, q, qs = ops.layernorm_modulate_quant(h, eps=self.norm2.eps, ln_weight=w2, ln_bias=b2, q_dtype=q2,
+                                                    want_y=q2 is None)
         h = p2._cross_attention(self.attn2, y if y is not None else h, ctx,
                                 prequant=(q, qs) if q is not None else None, resid=h)
         # 3. FFN: LN + modulate (+ quantise) -> up + GELU (epilogue) -> quantise -> down, h + gate * (.) (epilogue)

@@ -42,8 +42,15 @@ def denoise(pipe, latents: torch.Tensor, prompt_embeds: torch.Tensor,
     sigmas = flow_match_sigmas(num_inference_steps, flow_shift, num_train_timesteps).to(latents.device)
     use_cfg = negative_prompt_embeds is not None and guidance_scale > 1.0
     x = latents
+    steps = [(sigmas[i] * num_train_timesteps).reshape(1).expand(x.shape[0]) for i in range(num_inference_steps)]
+    if getattr(transformer, "enable_teacache", False) and hasattr(transformer, "condition_embedder"):
+        # the cache's decisions depend on the timestep embedding only: prepare them all with one host read
+        def embed(t):
+            temb, timestep_proj = transformer.condition_embedder(t, prompt_embeds, None)[:2]
+            return timestep_proj.unflatten(1, (6, -1)) if transformer.use_ref_steps else temb
+        teacache.plan_trajectory(transformer, steps, embed, calls_per_step=2 if use_cfg else 1)
     for i in range(num_inference_steps):
-        t = (sigmas[i] * num_train_timesteps).reshape(1).expand(x.shape[0])
+        t = steps[i]
         v = transformer(x, t, prompt_embeds, return_dict=False)[0]
         if use_cfg:
             v_u = transformer(x, t, negative_prompt_embeds, return_dict=False)[0]

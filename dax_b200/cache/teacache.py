@@ -42,10 +42,16 @@ def should_skip_forward_for_cached_states(self, **kwargs) -> bool:
         calc = True
         setattr(self, acc_name, 0)
     else:
-        prev = getattr(self, prev_name)
-        assert prev is not None, f"{prev_name} is not initialized"
-        # one host read per forward, as in the reference (the decision steers Python control flow)
-        rel = float(((inp - prev).abs().mean() / prev.abs().mean()).cpu().item())
+        plan = getattr(self, "_rel_l1_plan", None)
+        if plan is not None and self.cnt // plan["calls_per_step"] < len(plan["rel"]):
+            # distances of the whole trajectory were read back once, before the loop: no device
+            # synchronisation per forward
+            rel = plan["rel"][self.cnt // plan["calls_per_step"]]
+        else:
+            prev = getattr(self, prev_name)
+            assert prev is not None, f"{prev_name} is not initialized"
+            # one host read per forward, as in the reference (the decision steers Python control flow)
+            rel = float(((inp - prev).abs().mean() / prev.abs().mean()).cpu().item())
         acc = getattr(self, acc_name) + float(np.poly1d(self.coefficients)(rel))
         calc = acc >= self.teacache_thresh
         setattr(self, acc_name, 0 if calc else acc)
@@ -55,8 +61,27 @@ def should_skip_forward_for_cached_states(self, **kwargs) -> bool:
     return not calc
 
 
+@torch.no_grad()
+def plan_trajectory(transformer, timesteps, embed, calls_per_step: int = 2) -> None:
+    """Read the relative L1 distances of a whole denoising trajectory back in ONE device->host copy.
+
+    The quantity the cache accumulates depends on the timestep embedding alone (never on the latents), so
+    when the loop knows its timesteps in advance every decision can be prepared before the first forward.
+    ``embed(t)`` returns the modulation input the decision looks at (``timestep_proj`` with ``use_ref_steps``,
+    else ``temb``) for one timestep tensor; ``calls_per_step`` is 2 under classifier-free guidance (both
+    branches see the same timestep).  ``should_skip_forward_for_cached_states`` then takes its distance from the
+    plan instead of synchronising with the device at every forward; the per-forward read of the reference
+    (``dax/cache/teacache.py:58-65``) stays as the path for callers that do not plan."""
+    inps = torch.stack([embed(t).float() for t in timesteps], 0)
+    flat = inps.flatten(1)
+    rel = (flat[1:] - flat[:-1]).abs().mean(1) / flat[:-1].abs().mean(1)
+    transformer._rel_l1_plan = {"rel": [0.0] + [float(v) for v in rel.cpu()], "calls_per_step": calls_per_step}
+
+
 def reset_cache(pipe) -> None:
     t = pipe.transformer
+    if hasattr(t, "_rel_l1_plan"):
+        del t._rel_l1_plan
     if hasattr(t, "cnt"):
         t.cnt = 0
         for b in _BRANCHES:

@@ -203,6 +203,20 @@ def rmsnorm_rope_pack(x: torch.Tensor, *, norm_weight: Optional[torch.Tensor], d
         ldo = D
     if col_group is None:
         col_group = D
+    # the kernel reads the weight as 16-bit elements of x's dtype and the tables as fp32 [S_total, 64]
+    if norm_weight is not None and (norm_weight.dtype != x.dtype or norm_weight.numel() != D or not norm_weight.is_contiguous()):
+        raise ValueError(f"rmsnorm_rope_pack: norm_weight must be a contiguous [{D}] tensor of {x.dtype}, got "
+                         f"{tuple(norm_weight.shape)} {norm_weight.dtype}")
+    if (rope_cos is None) != (rope_sin is None):
+        raise ValueError("rmsnorm_rope_pack: rope_cos and rope_sin come together")
+    for tname, tab in (("rope_cos", rope_cos), ("rope_sin", rope_sin)):
+        if tab is not None and (tab.dtype != torch.float32 or tab.dim() != 2 or tab.shape[1] != 64 or not tab.is_contiguous()
+                                or token_offset + s > tab.shape[0]):
+            raise ValueError(f"rmsnorm_rope_pack: {tname} must be a contiguous fp32 [>= {token_offset + s}, 64] table, got "
+                             f"{tuple(tab.shape)} {tab.dtype}")
+    if row_sumsq is not None and (row_sumsq.dtype != torch.float32 or row_sumsq.dim() != 2 or row_sumsq.shape[0] < s
+                                  or not row_sumsq.is_contiguous()):
+        raise ValueError(f"rmsnorm_rope_pack: row_sumsq must be a contiguous fp32 [>= {s}, n] tensor")
     n_part = row_sumsq.shape[1] if row_sumsq is not None else 0
     tok = TRACE.begin("rmsnorm_rope_pack")
     check(load().dax_rmsnorm_rope_pack(x.data_ptr(), _dt(x.dtype), s, D, x.stride(0), _ptr(row_sumsq), n_part,
@@ -225,19 +239,24 @@ class AttentionPlan:
         self.B, self.heads, self.Sq, self.Sk, self.mode, self.workspace, self.dtype = B, heads, Sq, Sk, mode, workspace, dtype
 
 
-_WS_CACHE = {}
+_WS_CACHE = {}   # (device, B, heads, Sq, Sk, mode) -> buffer; insertion-ordered, a few most recent shapes
+_WS_CACHE_ENTRIES = 4
 
 
 def attn_workspace(B: int, heads: int, Sq: int, Sk: int, mode: int, device) -> torch.Tensor:
+    """Workspace of one attention shape.  A block alternates between self-attention and cross-attention, so a few
+    shapes stay cached; every plan of the same shape shares ONE buffer: a plan is valid until the next
+    ``attn_prepare`` of that shape (on the same stream)."""
     n = load().dax_attn_workspace_bytes(B, heads, Sq, Sk, mode)
     if n == 0:
         check(_lib.DAX_ERR_INVALID)
-    key = (str(device), n)
-    ws = _WS_CACHE.get(key)
+    key = (str(device), B, heads, Sq, Sk, mode)
+    ws = _WS_CACHE.pop(key, None)
     if ws is None:
-        _WS_CACHE.clear()
+        while len(_WS_CACHE) >= _WS_CACHE_ENTRIES:
+            _WS_CACHE.pop(next(iter(_WS_CACHE)))
         ws = torch.empty(n + 1024, dtype=torch.uint8, device=device)
-        _WS_CACHE[key] = ws
+    _WS_CACHE[key] = ws  # most recently used last
     off = (-ws.data_ptr()) % 1024
     return ws[off:off + n]
 

@@ -375,3 +375,55 @@ def wan_block(h, ctx, temb6, table6, attn1, attn2, norm2_w, norm2_b, ffn_up, ffn
     n = (layernorm(h, eps=eps) * (1 + c_scale) + c_shift).type_as(h)
     f = ffn_down(F.gelu(ffn_up(n), approximate="tanh"))
     return (h.float() + f.float() * c_gate).type_as(h)
+
+
+def dit_forward(latent: torch.Tensor, timestep: torch.Tensor, text: torch.Tensor, sd: dict, *, heads: int,
+                patch_size=(1, 2, 2), freq_dim: int = 256, weight_dtype=torch.int8, act_dtype=torch.int8,
+                eps: float = 1e-6) -> torch.Tensor:
+    """One denoising forward of a Wan-shaped DiT at world size 1, following ``new_forward``
+    (``dax/adapters/wan/transformer_adapter.py:51-179``): rotary table on the full latent (``:84``), patch
+    embedding as a strided convolution flattened to ``[B, S, D]`` (``:86-87``), condition embedder (``:89-97``:
+    sinusoidal timestep features -> MLP -> ``temb``; SiLU + linear -> the six modulation vectors; text MLP), the
+    block stack (``:130-136``) through ``wan_block``, the modulated output norm and projection (``:142-154``),
+    unpatchify (``:159-170``).  ``sd`` maps the transformer's parameter names (diffusers' naming) to tensors;
+    every linear inside the blocks is quantised the way ``quantize_transformer`` leaves it (``:227-234``), the
+    condition embedder and ``proj_out`` stay float.  The module definitions themselves are diffusers code
+    (absent from the reference tree): parity unpinned for them, see the header."""
+    dt = latent.dtype
+    B, _, f, h, w = latent.shape
+    pt, ph, pw = patch_size
+    grid = (f // pt, h // ph, w // pw)
+    freqs = rope_table(grid)
+
+    def lin(name, x):  # float linear: fp32 accumulate, rounded to the model dtype
+        b = sd.get(name + ".bias")
+        return F.linear(x.float(), sd[name + ".weight"].float(), None if b is None else b.float()).to(dt)
+
+    def qlin(name):
+        return QuantLinear(sd[name + ".weight"], sd.get(name + ".bias"), weight_dtype, act_dtype)
+
+    x = F.conv3d(latent.float(), sd["patch_embedding.weight"].float(), sd["patch_embedding.bias"].float(),
+                 stride=patch_size).to(dt).flatten(2).transpose(1, 2)
+    half = freq_dim // 2
+    fr = torch.exp(-math.log(10000.0) * torch.arange(half, dtype=torch.float32) / half)
+    ang = timestep.float()[:, None] * fr[None]
+    emb = torch.cat([torch.cos(ang), torch.sin(ang)], dim=-1).to(dt)
+    temb = lin("condition_embedder.time_embedder.2", F.silu(lin("condition_embedder.time_embedder.0", emb)))
+    timestep_proj = lin("condition_embedder.time_proj", F.silu(temb)).unflatten(1, (6, -1))
+    ctx = lin("condition_embedder.text_embedder.2",
+              F.gelu(lin("condition_embedder.text_embedder.0", text.to(dt)), approximate="tanh"))
+
+    n_layers = 1 + max(int(k.split(".")[1]) for k in sd if k.startswith("blocks."))
+    for i in range(n_layers):
+        p = f"blocks.{i}."
+        attn = lambda a: (qlin(p + a + ".to_q"), qlin(p + a + ".to_k"), qlin(p + a + ".to_v"), qlin(p + a + ".to_out.0"),
+                          sd[p + a + ".norm_q.weight"], sd[p + a + ".norm_k.weight"])
+        x = wan_block(x, ctx, timestep_proj, sd[p + "scale_shift_table"], attn("attn1"), attn("attn2"),
+                      sd.get(p + "norm2.weight"), sd.get(p + "norm2.bias"), qlin(p + "ffn.net.0.proj"),
+                      qlin(p + "ffn.net.2"), heads, freqs, eps)
+
+    shift, scale = (sd["scale_shift_table"].float() + temb.float().unsqueeze(1)).chunk(2, dim=1)
+    x = (layernorm(x, eps=eps) * (1 + scale) + shift).to(dt)
+    x = lin("proj_out", x)
+    x = x.reshape(B, grid[0], grid[1], grid[2], pt, ph, pw, -1).permute(0, 7, 1, 4, 2, 5, 3, 6)
+    return x.flatten(6, 7).flatten(4, 5).flatten(2, 3)

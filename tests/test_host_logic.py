@@ -176,3 +176,36 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "library_path", lambda: str(tmp_path / "absent.so"))
     with pytest.raises(_lib.DaxLibraryError, match="no CPU"):
         _lib.load()
+
+
+def test_rope_table_cache_survives_address_reuse():
+    """Two rotary tables of identical shape and different content, the second allocated after the first was
+    dropped (the allocator may hand out the same address): each gets its own cos/sin; an in-place update of a
+    cached table is noticed through the version counter."""
+    from dax_b200.adapters.wan.attn_adapter import _rope_tables
+    from dax_b200.adapters.wan.modules import wan_rope_table
+    seen = []
+    for grid in ((2, 3, 4), (2, 4, 3), (4, 3, 2)):
+        table = wan_rope_table(grid).clone()
+        cos, sin = _rope_tables(table)
+        want = torch.view_as_real(table.reshape(-1, 64))
+        assert torch.equal(cos, want[..., 0].float()) and torch.equal(sin, want[..., 1].float())
+        seen.append(cos)
+        del table
+    assert not torch.equal(seen[0], seen[1])
+    table = wan_rope_table((2, 3, 4)).clone()
+    cos0, _ = _rope_tables(table)
+    table.mul_(1j)  # rotate every entry by 90 degrees, in place
+    cos1, sin1 = _rope_tables(table)
+    assert torch.allclose(cos1, -torch.view_as_real(wan_rope_table((2, 3, 4)).reshape(-1, 64))[..., 1].float())
+    assert not torch.equal(cos0, cos1)
+
+
+def test_unknown_cache_strategy_disables_teacache():
+    from dax_b200.adapters.wan.transformer_adapter import replace_transformer
+
+    class T(nn.Module):
+        pass
+
+    t = replace_transformer(T(), cache_strategy="something_else")
+    assert type(t).enable_teacache is False

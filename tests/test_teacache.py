@@ -108,3 +108,28 @@ def test_denoise_loop_integrates_and_drives_the_cache():
     pipe.transformer.calls.clear()
     denoise(pipe, x0, pos, None, num_inference_steps=4)
     assert len(pipe.transformer.calls) == 4
+
+
+def test_planned_trajectory_gives_the_same_decisions(golden_dir):
+    """The distances of a whole trajectory read back once (plan_trajectory) lead to the decisions and
+    accumulators the per-forward host read produces, call for call (both guidance branches see the same
+    timestep embedding, as in the denoising loop)."""
+    g = torch.load(os.path.join(golden_dir, "teacache.pt"))
+    per_step = g["inputs"][::2]
+    calls = [tp for tp in per_step for _ in range(2)]
+    lazy, planned = fresh(), fresh()
+    it = iter(per_step)
+    teacache.plan_trajectory(planned, range(len(per_step)), lambda _t: next(it), calls_per_step=2)
+    skips = []
+    for i, tp in enumerate(calls):
+        a = teacache.should_skip_forward_for_cached_states(lazy, timestep_proj=tp, temb=tp[:, 0])
+        b = teacache.should_skip_forward_for_cached_states(planned, timestep_proj=tp, temb=tp[:, 0])
+        assert a == b, f"call {i}"
+        skips.append(a)
+        for name in ("accumulated_rel_l1_distance_even", "accumulated_rel_l1_distance_odd"):
+            assert abs(float(getattr(lazy, name)) - float(getattr(planned, name))) < 1e-6
+    assert any(skips) and not all(skips)
+    holder = Holder()
+    holder.transformer = planned
+    teacache.reset_cache(holder)
+    assert not hasattr(planned, "_rel_l1_plan")
