@@ -77,14 +77,33 @@ def _rope_tables(rotary_emb: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return cos, sin
 
 
+_EXCHANGES: Dict[int, UlyssesExchange] = {}
+
+
+def shared_exchange() -> UlyssesExchange:
+    """The one exchange object of the sequence-parallel group, shared by every processor of the process."""
+    ps = para_dist.parallel_state
+    group = ps.get_sequence_parallel_group()
+    x = _EXCHANGES.get(id(group))
+    if x is None:
+        x = _EXCHANGES[id(group)] = UlyssesExchange(group, ps.get_sequence_parallel_size(), ps.get_sequence_parallel_rank())
+    return x
+
+
 class DAXWanAttnProcessor2_0:
-    def __init__(self, sp_size: int = 1, overlap_comm: bool = False, attention_mode: str = "sage",
-                 qkv_chunks: int = 4, o_micro_batches: int = 2, o_split: str = "auto"):
-        """``sp_size`` / ``overlap_comm`` as in the reference.  ``attention_mode``: "sage" (INT8 Q.K^T,
-        FP8 P.V) or "f16" (fp16 contractions).  ``qkv_chunks``: token chunks of the Q/K/V projections
-        whose exchange overlaps the next chunk's GEMMs; ``o_micro_batches``: micro-batches of the O
+    def __init__(self, sp_size: int = 1, overlap_comm: bool = False, attention_mode: str = "bf16",
+                 qkv_chunks: int = 4, o_micro_batches: int = 2, o_split: str = "auto",
+                 sequence_parallel: Optional[bool] = None):
+        """``sp_size`` / ``overlap_comm`` as in the reference.  ``attention_mode``: "bf16" (bf16 contractions: the
+        mode within rel-L2 1e-2 of fp32 SDPA, default), "sage" (INT8 Q.K^T, FP8 P.V: the reference backend's
+        arithmetic) or "int8_bf16".  ``qkv_chunks``: token chunks of the Q/K/V
+        projections whose exchange overlaps the next chunk's GEMMs; ``o_micro_batches``: micro-batches of the O
         path (2 in the reference); ``o_split``: how the O path is cut, "rows" (the reference's scheme),
-        "ranks" (by groups of destination ranks) or "auto" (whichever needs fewer rounds of attention CTAs)."""
+        "ranks" (by groups of destination ranks) or "auto" (whichever needs fewer rounds of attention CTAs).
+        ``sequence_parallel``: None follows the process-wide parallel state (the reference's behaviour); False
+        keeps this processor local even when the state is initialised (an un-sharded layer run next to a sharded
+        one, e.g. to check the sharded result)."""
+        self.sequence_parallel = sequence_parallel
         if o_split not in ("auto", "rows", "ranks"):
             raise ValueError("o_split must be 'auto', 'rows' or 'ranks'")
         self.o_split = o_split
@@ -99,12 +118,10 @@ class DAXWanAttnProcessor2_0:
 
     # ------------------------------------------------------------------------------------------
     def _exchange(self) -> Optional[UlyssesExchange]:
-        if not para_dist.parallel_state.is_enable_sequence_parallel():
+        if self.sequence_parallel is False or not para_dist.parallel_state.is_enable_sequence_parallel():
             return None
         if self._xchg is None:
-            ps = para_dist.parallel_state
-            self._xchg = UlyssesExchange(ps.get_sequence_parallel_group(), ps.get_sequence_parallel_size(),
-                                         ps.get_sequence_parallel_rank())
+            self._xchg = shared_exchange()
         return self._xchg
 
     @staticmethod

@@ -13,9 +13,11 @@ log = logging.getLogger("dax_b200")
 
 
 def optimize_pipe(pipe, sequence_parallel=True, compile=True, overlap_comm=True, int8_linear=False,
-                  cache_strategy=None, fp8_linear=False, attention_mode="sage", fuse_blocks=True, **cache_params):
+                  cache_strategy=None, fp8_linear=False, attention_mode="bf16", fuse_blocks=True, **cache_params):
     """Same switches as the reference.  ``compile`` is accepted for signature compatibility and has
-    no effect: every kernel is precompiled CUDA, nothing is traced.  ``fp8_linear`` (not in the
+    no effect: every kernel is precompiled CUDA, nothing is traced.  ``attention_mode``: precision of the attention kernel's two contractions, "bf16" (default, within
+    rel-L2 1e-2 of fp32 SDPA), "sage" (INT8 Q.K^T + FP8 P.V, what the reference's SAGE_ATTN backend computes) or
+    "int8_bf16".  ``fp8_linear`` (not in the
     reference's signature, where FP8 is reachable only through ``quantize_dynamic``) selects e4m3
     activations x e4m3 weights; ``fuse_blocks`` binds the fused CUDA forward on every Wan block (LayerNorm /
     modulation / GELU / gated residuals ride in the quantiser and GEMM kernels)."""

@@ -66,8 +66,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // Poll limit of every spin in this library. try_wait itself blocks for a hardware-defined
-// slice (on the order of a microsecond), so this is seconds, not cycles.
-constexpr uint32_t kSpinLimit = 1u << 22;
+// slice (on the order of a microsecond), so this is seconds, not cycles.  A build may lower it
+// (-DDAX_SPIN_LIMIT=n): the test-suite does, to watch a wait run out within milliseconds.
+#ifndef DAX_SPIN_LIMIT
+#define DAX_SPIN_LIMIT (1u << 22)
+#endif
+constexpr uint32_t kSpinLimit = DAX_SPIN_LIMIT;
 
 // Bounded wait. `abort_flag` is a CTA-shared word any role sets when it gave up; every waiter
 // watches it so that one timeout drains the whole CTA instead of leaving siblings spinning.

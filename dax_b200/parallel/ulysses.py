@@ -40,13 +40,24 @@ class _Works:
 
 
 class UlyssesExchange:
+    """``skip_comm`` and ``recorded`` exist for measuring how much of the exchange time is hidden:
+    with ``skip_comm`` the point-to-point operations are left out (local copies still happen; the results are
+    then meaningless), and while ``recorded`` is a list every exchange call is appended to it as a closure that
+    re-issues the same operations on the same buffers, so that a step's exchanges can be replayed alone."""
+
     def __init__(self, group, size: int, rank: int):
         self.group, self.P, self.rank = group, size, rank
         self.global_ranks = (dist.get_process_group_ranks(group) if group is not None and size > 1
                              else list(range(size)))
+        self.skip_comm = False
+        self.recorded: Optional[list] = None
 
     def _run(self, ops, async_op: bool):
-        if not ops:
+        if self.recorded is not None and ops:
+            kinds = [(o.op, o.tensor, o.peer) for o in ops]
+            group = self.group
+            self.recorded.append(lambda: _Works(dist.batch_isend_irecv([dist.P2POp(k, t, p, group) for k, t, p in kinds])))
+        if not ops or self.skip_comm:
             return _Done()
         works = _Works(dist.batch_isend_irecv(ops))
         if not async_op:

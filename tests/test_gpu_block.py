@@ -74,9 +74,10 @@ def test_processor_config1(wan, linear, mode):
     y = attn(x.to(DEV), rotary_emb=fr.to(DEV))
     assert y.shape == (1, S, D) and y.dtype == torch.bfloat16
     got = y.float().cpu()
-    # Attention within its own bound (tests/test_gpu_kernels.py); at block level the O projection
-    # re-quantises the attention output per token, and a 2e-3 perturbation of an FP8 (3-bit mantissa) input
-    # flips enough rounding decisions to move the block output by about 1e-2, so the FP8-linear block gets 2e-2.
+    # The 16-bit attention mode is held to the stated tolerance (rel-L2 <= 1e-2) with INT8 linears; the block with
+    # FP8 linears gets 2e-2: the O projection re-quantises the attention output per token, and a 2e-3 perturbation
+    # of an FP8 (3-bit mantissa) input flips enough rounding decisions to move the block output by about 1e-2.
+    # "sage" (INT8 Q.K^T + FP8 P.V) does NOT meet the stated tolerance on Gaussian data: labelled bound 5e-2.
     tol = (1e-2 if linear == "int8" else 2e-2) if mode == "f16" else 5e-2
     assert O.cosine(got, ref) >= 0.999
     assert O.rel_l2(got, ref) <= tol, O.rel_l2(got, ref)

@@ -293,10 +293,10 @@ def test_attention_high_accuracy_mode(ops, S):
 
 @pytest.mark.parametrize("S", [1, 128, 256, 1000, 2049])
 def test_attention_sage_mode(ops, S):
-    """INT8 Q.K^T + FP8 P.V: cosine >= 0.999 against fp32 SDPA.  Single-term FP8 P and V carry about
-    2.6 % relative rounding error each, so on Gaussian data (outputs are small residual sums) rel-L2
-    sits near 3.7e-2; the kernel must stay within 5e-2 and track the oracle's model of the same
-    quantisation closely."""
+    """INT8 Q.K^T + FP8 P.V.  THIS MODE DOES NOT MEET the stated attention tolerance (rel-L2 <= 1e-2): single-term
+    FP8 P and V carry about 2.6 % relative rounding error each, so on Gaussian data (outputs are small residual
+    sums) rel-L2 sits near 3.7e-2 for any kernel with these operand formats.  Labelled bounds: cosine >= 0.999,
+    rel-L2 <= 5e-2, and within 4e-2 of the oracle's model of the same quantisation."""
     q, k, v = qkv(1, 3, S, S)
     ref = O.sdpa_fp32(q, k, v)
     o = ops.attention(q.to(DEV), k.to(DEV), v.to(DEV), mode="sage").float().cpu()
@@ -308,8 +308,9 @@ def test_attention_sage_mode(ops, S):
 
 @pytest.mark.parametrize("S", [1, 128, 1000, 2049])
 def test_attention_int8_bf16_mode(ops, S):
-    """INT8 Q.K^T + bf16 P.V (V unquantised): the remaining error is the INT8 rounding of Q and K, about
-    1e-2 rel-L2 on Gaussian data (per-token Q scales, per-128-token K scales), cosine >= 0.9999."""
+    """INT8 Q.K^T + bf16 P.V (V unquantised).  NOT HELD to the stated tolerance either: the INT8 rounding of Q and K
+    alone costs about 1e-2 rel-L2 on Gaussian data (per-token Q scales, per-128-token K scales), i.e. it sits ON
+    the bound.  Labelled bounds: rel-L2 <= 2e-2, cosine >= 0.9999, within 1e-2 of the oracle's model."""
     q, k, v = qkv(1, 3, S, S)
     ref = O.sdpa_fp32(q, k, v)
     o = ops.attention(q.to(DEV), k.to(DEV), v.to(DEV), mode="int8_bf16").float().cpu()

@@ -1,5 +1,6 @@
 """Sequence-parallel processor on 2 (and 4) GPUs against the single-GPU result with the same weights:
-both `overlap_comm` settings, an odd local token count (uneven chunks and micro-batches).  Skipped on a
+both `overlap_comm` settings and both O-path splits, an odd local token count (63: uneven chunks and
+micro-batches), the 16-bit attention mode with INT8 linears and the INT8/FP8 mode with FP8 linears.  Skipped on a
 one-GPU box.  Ranks are child processes over NCCL with NVLS off; no rank leaves with work in flight."""
 import os
 import socket
@@ -36,7 +37,7 @@ def _inputs(S, D, grid, seed=5):
     return torch.randn(1, S, D, generator=g).bfloat16(), wan_rope_table(grid)
 
 
-def _worker(rank, world, port, S, D, H, grid, q):
+def _worker(rank, world, port, S, D, H, grid, q, mode, linear):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       LOCAL_RANK=str(rank), LOCAL_WORLD_SIZE=str(world), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
@@ -53,8 +54,8 @@ def _worker(rank, world, port, S, D, H, grid, q):
             holder = torch.nn.Module()
             holder.blocks = torch.nn.ModuleList([_build(D, H, 3)])
             pipe = _Pipe(holder.to(dev))
-            optimize_pipe(pipe, sequence_parallel=True, compile=False, overlap_comm=bool(overlap), int8_linear=True,
-                          attention_mode="f16")
+            optimize_pipe(pipe, sequence_parallel=True, compile=False, overlap_comm=bool(overlap),
+                          int8_linear=linear == "int8", fp8_linear=linear == "fp8", attention_mode=mode)
             if overlap == "ranks":  # O path cut by groups of destination ranks instead of row slices
                 holder.blocks[0].processor.o_split = "ranks"
             y = holder.blocks[0](x[:, rank * s:(rank + 1) * s].to(dev), rotary_emb=rope.to(dev))
@@ -71,27 +72,29 @@ def _worker(rank, world, port, S, D, H, grid, q):
             dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("mode,linear", [("f16", "int8"), ("sage", "fp8")])
 @pytest.mark.parametrize("world", [2, 4])
-def test_sequence_parallel_matches_single_gpu(built_library, world):
+def test_sequence_parallel_matches_single_gpu(built_library, world, mode, linear):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     from dax_b200.adapters.wan import optimize_pipe
     from dax_b200.adapters.wan.modules import _Pipe
     from oracle import dax_oracle as O
     D, H = 1024, 8
-    grid = (2, 7, world * 9)      # S = 126 * world tokens: odd local length 63 * 2
+    grid = (1, 7, world * 9)      # S = 63 * world tokens: odd local length 63
     S = grid[0] * grid[1] * grid[2]
     x, rope = _inputs(S, D, grid)
     holder = torch.nn.Module()
     holder.blocks = torch.nn.ModuleList([_build(D, H, 3)])
     pipe = _Pipe(holder.to("cuda:0"))
-    optimize_pipe(pipe, sequence_parallel=False, compile=False, overlap_comm=False, int8_linear=True, attention_mode="f16")
+    optimize_pipe(pipe, sequence_parallel=False, compile=False, overlap_comm=False, int8_linear=linear == "int8",
+                  fp8_linear=linear == "fp8", attention_mode=mode)
     ref = holder.blocks[0](x.to("cuda:0"), rotary_emb=rope.to("cuda:0")).float().cpu()
 
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, S, D, H, grid, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, S, D, H, grid, q, mode, linear)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=300) for _ in range(world)]
