@@ -16,7 +16,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 LIBNAME = "libdax_b200.so"
 
-SOURCES = ["capi.cu", "quant.cu", "gemm.cu", "linear.cu", "rope_pack.cu", "dit_block.cu", "attn_prep.cu", "attn.cu"]
+SOURCES = ["capi.cu", "quant.cu", "gemm.cu", "linear.cu", "rope_pack.cu", "dit_block.cu", "attn_prep.cu", "attn.cu", "attn_tmem.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -29,6 +29,7 @@
 // Operands come from the workspace written by the prepare step (attn_prep.cu): every tile is a set
 // of [128 rows x 128 bytes] boxes, so one shared-memory descriptor form serves Q, K, P and V^T.
 #include <climits>
+#include <cstdlib>
 
 #include "attn_common.cuh"
 #include "sm100_ptx.cuh"
@@ -89,20 +90,6 @@ struct Smem {
   static constexpr int OFF_VSCALE = OFF_BAR + 256;
   static constexpr int OFF_XCHG = OFF_VSCALE + 512;           // [2 tiles][2 parities][2 halves][128 rows] x 8 B
   static constexpr int TOTAL = OFF_XCHG + 2 * 2 * 2 * 128 * 8 + 1024 /*alignment slack*/;
-};
-
-struct AttnParams {
-  const float* q_scale;  // [BH, Sq_pad]
-  const float* k_scale;  // [BH, Sk_pad/128]
-  const float* v_scale;  // [BH, 128]
-  void* o;
-  int* status;
-  int64_t o_sb, o_sh, o_st;  // element strides of o: batch, head, token
-  int heads;
-  int Sq, Sk, Sq_pad, Sk_pad;
-  int q_begin, q_end;      // first query range
-  int n_ranges, range_stride, tiles_per_range;
-  int out_bf16;
 };
 
 // K-major descriptor pair advance: `sub` selects the 16 KB box, `k` the 32-byte step inside it.
@@ -599,6 +586,8 @@ extern "C" int dax_attn_forward(void* o, int dtype, int64_t B, int64_t heads, in
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (mode == DAX_ATTN_QK_I8_PV_F8) return launch_fwd<DAX_ATTN_QK_I8_PV_F8>(ws, p, B * heads, st);
   if (mode == DAX_ATTN_QK_I8_PV_BF16) return launch_fwd<DAX_ATTN_QK_I8_PV_BF16>(ws, p, B * heads, st);
-  return launch_fwd<DAX_ATTN_QK_BF16_PV_BF16>(ws, p, B * heads, st);
+  static const bool legacy = [] { const char* e = getenv("DAX_ATTN_BF16_LEGACY"); return e && e[0] == '1'; }();
+  if (legacy) return launch_fwd<DAX_ATTN_QK_BF16_PV_BF16>(ws, p, B * heads, st);
+  return launch_attn_fwd_tmem_p(ws, p, B * heads, st);
 }
 

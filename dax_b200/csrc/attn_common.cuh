@@ -29,6 +29,21 @@ struct AttnWorkspace {
   size_t bytes;
 };
 
+// Arguments of the forward kernels.
+struct AttnParams {
+  const float* q_scale;  // [BH, Sq_pad]
+  const float* k_scale;  // [BH, Sk_pad/128]
+  const float* v_scale;  // [BH, 128]
+  void* o;
+  int* status;
+  int64_t o_sb, o_sh, o_st;  // element strides of o: batch, head, token
+  int heads;
+  int Sq, Sk, Sq_pad, Sk_pad;
+  int q_begin, q_end;      // first query range
+  int n_ranges, range_stride, tiles_per_range;
+  int out_bf16;
+};
+
 inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 
 // bytes per element of the Q/K operands and of the P/V operands for a mode
@@ -78,5 +93,8 @@ inline int attn_workspace_layout(int64_t B, int64_t heads, int64_t Sq, int64_t S
   }
   return DAX_OK;
 }
+
+// bf16 Q.K^T + bf16 P.V with the probabilities kept in tensor memory (attn_tmem.cu)
+int launch_attn_fwd_tmem_p(const AttnWorkspace& ws, const AttnParams& p, int64_t BH, cudaStream_t st);
 
 }  // namespace dax
