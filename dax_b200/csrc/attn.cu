@@ -1,9 +1,9 @@
 // Quantised non-causal flash attention for head_dim 128 on tcgen05 / TMEM / TMA.
 //
-// Two precisions of the two contractions (template parameters, chosen per call):
+// The two modes with INT8 scores (template parameter, chosen per call):
 //   INT8 Q.K^T (kind::i8, int32 accumulators)  + FP8 e4m3 P.V (kind::f8f6f4, fp32 accumulators)
-//   bf16 Q.K^T (kind::f16, fp32 accumulators)  + bf16 P.V
 //   INT8 Q.K^T                                 + bf16 P.V   (V unquantised; P -> bf16 by truncation)
+// (the mode with bf16 scores, bf16 Q.K^T + bf16 P.V, is the kernel in attn_tmem.cu)
 // A CTA owns 256 query rows of one (batch, head): two 128-row tiles X = 0, 1 that ping-pong so
 // that the tensor pipe works on one tile while the softmax warps work on the other.
 //
@@ -12,7 +12,7 @@
 //   warps 8..15   the same for tile 1
 //   warp  16      TMA producer: both Q tiles once, then K_0, V_0, K_1, V_1, ... through a ring
 //   warps 17..    MMA issuers, one thread each: two (one per tile: Q.K^T of the next KV tile, then P.V of this
-//                 one) or three (Q.K^T of both tiles; P.V of tile 0; P.V of tile 1), see AttnCfg
+//                 one) or, with 16-bit P.V, three (Q.K^T of both tiles; P.V of tile 0; P.V of tile 1), see AttnCfg
 // Four softmax warps per scheduler instead of two: the softmax is a chain of dependent fixed-latency
 // operations around a 16-per-clock exp unit, and only more resident warps hide that latency.  The two
 // threads of a row agree on the row maximum through a sequence-stamped shared-memory slot (no CTA or
@@ -29,7 +29,6 @@
 // Operands come from the workspace written by the prepare step (attn_prep.cu): every tile is a set
 // of [128 rows x 128 bytes] boxes, so one shared-memory descriptor form serves Q, K, P and V^T.
 #include <climits>
-#include <cstdlib>
 
 #include "attn_common.cuh"
 #include "sm100_ptx.cuh"
@@ -49,14 +48,6 @@ template <> struct AttnCfg<DAX_ATTN_QK_I8_PV_F8> {
   static constexpr int ISSUERS = 2;
   static constexpr float TAU = 0.f;          // P is scaled to the e4m3 range: the row max must be exact
   static constexpr float PBIAS = 8.8073549f; // log2(448): P in (0, 448]
-};
-template <> struct AttnCfg<DAX_ATTN_QK_BF16_PV_BF16> {
-  static constexpr int QK_KIND = KIND_F16, PV_KIND = KIND_F16;
-  static constexpr int EQ = 2, EP = 2;
-  static constexpr int NSLOT = 2;            // 2 x 32 KB: shared memory is full (Q 64 KB + P 64 KB + ring 64 KB)
-  static constexpr int ISSUERS = 3;
-  static constexpr float TAU = 8.f;          // lazy rescale: P <= 2^8, far inside the bf16 range
-  static constexpr float PBIAS = 0.f;
 };
 template <> struct AttnCfg<DAX_ATTN_QK_I8_PV_BF16> {
   static constexpr int QK_KIND = KIND_I8, PV_KIND = KIND_F16;
@@ -586,8 +577,6 @@ extern "C" int dax_attn_forward(void* o, int dtype, int64_t B, int64_t heads, in
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (mode == DAX_ATTN_QK_I8_PV_F8) return launch_fwd<DAX_ATTN_QK_I8_PV_F8>(ws, p, B * heads, st);
   if (mode == DAX_ATTN_QK_I8_PV_BF16) return launch_fwd<DAX_ATTN_QK_I8_PV_BF16>(ws, p, B * heads, st);
-  static const bool legacy = [] { const char* e = getenv("DAX_ATTN_BF16_LEGACY"); return e && e[0] == '1'; }();
-  if (legacy) return launch_fwd<DAX_ATTN_QK_BF16_PV_BF16>(ws, p, B * heads, st);
-  return launch_attn_fwd_tmem_p(ws, p, B * heads, st);
+  return launch_attn_fwd_tmem_p(ws, p, B * heads, st);  // bf16 Q.K^T + bf16 P.V: attn_tmem.cu
 }
 

@@ -7,18 +7,20 @@
 //                 row sum stay inside the thread: no shuffle, no shared-memory exchange)
 //   warps 4..7    the same for tile 1
 //   warp  8       TMA producer: both Q tiles once, then K_0, V_0, K_1, V_1, ... through a ring of five 32 KB slots
-//   warp  9, 10   MMA issuer of tile 0 / tile 1 (one thread each)
+//   warp  9, 10   MMA issuers: warp 9 every Q.K^T, warp 10 every P.V (the warp runs the loop, one elected lane issues)
 //   warp  11      owns the tensor-memory allocation
 // The softmax warps raise their register budget with setmaxnreg (a row of 128 fp32 scores lives in registers), the
 // other four warps lower theirs.
 //
-// Tensor memory (512 columns): S_0 [0,128)  S_1 [128,256)  O_0 [256,384)  O_1 [384,512); P_X (bf16, 64 columns)
-// overlays columns [64,128) of S_X.  Per tile the chain is
-//     S_X(j) = Q_X.K_j^T  ->  softmax: S_X(j) -> registers -> P_X(j) -> tensor memory  ->  O_X += P_X(j).V_j
-//                         ->  S_X(j+1) = Q_X.K_{j+1}^T  (issued behind P.V by the same thread: the tensor pipe runs a
-//                             thread's instructions in order, so the overlay is safe)
-// and the two tiles run half a period apart by themselves: while one is in its softmax phase (exponential unit) the
-// other is in its MMA phase (tensor pipe).  Shared memory holds only Q (64 KB) and the K/V ring (160 KB).
+// Tensor memory (512 columns): S [0,128) (ONE score buffer, used by the two tiles in turn)  P_0 [128,192)
+// P_1 [192,256) (bf16, 64 columns each)  O_0 [256,384)  O_1 [384,512).  Per KV tile j and query tile X:
+//     S = Q_X.K_j^T  ->  the softmax warps of X copy S into registers and release it at once (s_free), so the other
+//                        tile's Q.K^T follows immediately;  row maximum, exponentials, P_X(j) -> tensor memory
+//                    ->  O_X += P_X(j).V_j   (pv_done)
+// The score buffer is busy only from the issue of a Q.K^T to the moment its 128 columns are in registers (about 800
+// clocks), twice per period, so sharing it costs nothing, and because P has columns of its own no product ever waits
+// for the softmax of its own tile: the exponential unit and the tensor pipe both run continuously.
+// Shared memory holds only Q (64 KB) and the K/V ring (160 KB).
 //
 // Operands come from the workspace written by the prepare step (attn_prep.cu) exactly as for the kernels in attn.cu.
 #include <climits>
@@ -41,8 +43,8 @@ constexpr int OFF_RING = OFF_Q + 2 * TILE_BYTES;
 constexpr int OFF_BAR = OFF_RING + NSLOT * TILE_BYTES;
 constexpr int SMEM_TOTAL = OFF_BAR + 256 + 1024 /*alignment slack*/;
 
-__device__ __forceinline__ void reg_alloc_224() { asm volatile("setmaxnreg.inc.sync.aligned.u32 224;"); }
-__device__ __forceinline__ void reg_dealloc_56() { asm volatile("setmaxnreg.dec.sync.aligned.u32 56;"); }
+__device__ __forceinline__ void reg_alloc_216() { asm volatile("setmaxnreg.inc.sync.aligned.u32 216;"); }
+__device__ __forceinline__ void reg_dealloc_72() { asm volatile("setmaxnreg.dec.sync.aligned.u32 72;"); }
 
 // D[tmem] (+)= A[tmem] * B[smem]^T, kind::f16, issued by ONE thread.  A: 128 lanes x (K/2) columns, two 16-bit
 // elements of consecutive K per 32-bit cell.
@@ -83,10 +85,11 @@ attn_fwd_tmem_p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   uint64_t* q_full = bars;                  // [1]
   uint64_t* kv_full = bars + 1;             // [NSLOT]
   uint64_t* kv_empty = kv_full + NSLOT;     // [NSLOT] released by two MMA commits (one per query tile)
-  uint64_t* s_full = kv_empty + NSLOT;      // [2]  MMA -> softmax: S_X(j) complete (and with it P_X(j-1).V_{j-1})
-  uint64_t* p_full = s_full + 2;            // [2]  softmax -> MMA: P_X(j) is in tensor memory, O_X rescaled
-  uint64_t* o_done = p_full + 2;            // [2]  MMA -> softmax: the last P.V of the tile has completed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
+  uint64_t* s_full = kv_empty + NSLOT;      // [2]  MMA -> softmax of X: S holds Q_X.K_j^T
+  uint64_t* s_free = s_full + 2;            // [1]  softmax -> MMA: S is in registers (uses alternate: tile 0, tile 1, ...)
+  uint64_t* p_full = s_free + 1;            // [2]  softmax -> MMA: P_X(j) is in tensor memory, O_X rescaled
+  uint64_t* pv_done = p_full + 2;           // [2]  MMA -> softmax: P_X(j).V_j complete, P_X and O_X are at rest
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -103,10 +106,11 @@ attn_fwd_tmem_p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 2);
     }
+    mbar_init(s_free, 4);          // one arrival per softmax warp of the tile that read S
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 4);  // one arrival per softmax warp of the tile
-      mbar_init(&o_done[i], 1);
+      mbar_init(&pv_done[i], 1);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -121,7 +125,7 @@ attn_fwd_tmem_p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp >= PRODUCER_WARP) {
-    reg_dealloc_56();
+    reg_dealloc_72();
     if (warp == PRODUCER_WARP) {
       // ---------------------------------------------------------------- TMA producer
       if (lane == 0) {
@@ -149,63 +153,78 @@ attn_fwd_tmem_p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
       }
     } else if (warp < TMEM_WARP) {
-      // ---------------------------------------------------------------- MMA issuer of tile x (one thread)
-      if (lane == 0) {
-        const int x = warp - ISSUER_WARP0;
+      // ---------------------------------------------------------------- MMA issuers
+      // The whole warp runs the loops (uniform control flow, every lane polls the barriers); one elected lane
+      // issues the tensor-core instructions and the commits.
+      {
+        const bool leader = elect_one();
         constexpr uint32_t idesc = make_idesc(1, 1, 1, 128, 128);  // bf16 x bf16 -> f32, M = N = 128
-        const uint64_t q_desc = make_desc_k_sw128(smem_u32(smem + OFF_Q + x * TILE_BYTES));
+        const uint32_t q_base = smem_u32(smem + OFF_Q);
         const uint32_t ring = smem_u32(smem + OFF_RING);
-        const uint32_t s_tm = tmem_base + x * 128;
-        const uint32_t p_tm = s_tm + 64;
-        const uint32_t o_tm = tmem_base + 256 + x * 128;
-        // S_x(j) = Q_x . K_j^T : 8 steps of 16 channels; box `sub` holds channels [64 sub, 64 sub + 64)
-        auto issue_qk = [&](int j) -> bool {
+        const uint32_t s_tm = tmem_base;
+        // S = Q_x . K_j^T : 8 steps of 16 channels; box `sub` holds channels [64 sub, 64 sub + 64).  Use number
+        // u = 2 j + x of the shared score buffer: it must have been read by the previous user.
+        auto issue_qk = [&](int x, int j) -> bool {
           const uint32_t seq = 2 * j, slot = seq % NSLOT, ph = (seq / NSLOT) & 1u;
+          const int u = 2 * j + x;
           if (!mbar_wait(&kv_full[slot], ph, abort_flag)) return false;
+          if (u > 0 && !mbar_wait(s_free, (u - 1) & 1u, abort_flag)) return false;
           tc_fence_after_sync();
+          const uint64_t q_desc = make_desc_k_sw128(q_base + x * TILE_BYTES);
           const uint64_t k_desc = make_desc_k_sw128(ring + slot * TILE_BYTES);
+          if (leader) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const uint64_t adv = static_cast<uint64_t>((i >> 2) * (BOX_BYTES >> 4) + 2 * (i & 3));
-            umma_ss<KIND_F16>(s_tm, q_desc + adv, k_desc + adv, idesc, i != 0 ? 1u : 0u);
+            for (int i = 0; i < 8; ++i) {
+              const uint64_t adv = static_cast<uint64_t>((i >> 2) * (BOX_BYTES >> 4) + 2 * (i & 3));
+              umma_ss<KIND_F16>(s_tm, q_desc + adv, k_desc + adv, idesc, i != 0 ? 1u : 0u);
+            }
+            umma_commit(&s_full[x]);
+            umma_commit(&kv_empty[slot]);
           }
-          umma_commit(&s_full[x]);
-          umma_commit(&kv_empty[slot]);
+          __syncwarp();
           return true;
         };
         // O_x += P_x(j) . V_j : 8 steps of 16 keys; A from tensor memory (8 columns per step), box `sub` of V^T
         // holds keys [64 sub, 64 sub + 64)
-        auto issue_pv = [&](int j) -> bool {
+        auto issue_pv = [&](int x, int j) -> bool {
           const uint32_t seq = 2 * j + 1, slot = seq % NSLOT, ph = (seq / NSLOT) & 1u;
           if (!mbar_wait(&kv_full[slot], ph, abort_flag)) return false;
           if (!mbar_wait(&p_full[x], j & 1u, abort_flag)) return false;
           tc_fence_after_sync();
           const uint64_t v_desc = make_desc_k_sw128(ring + slot * TILE_BYTES);
+          const uint32_t p_tm = tmem_base + 128 + x * 64;
+          const uint32_t o_tm = tmem_base + 256 + x * 128;
+          if (leader) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const uint64_t adv = static_cast<uint64_t>((i >> 2) * (BOX_BYTES >> 4) + 2 * (i & 3));
-            umma_ts_f16(o_tm, p_tm + 8 * i, v_desc + adv, idesc, (j > 0 || i != 0) ? 1u : 0u);
+            for (int i = 0; i < 8; ++i) {
+              const uint64_t adv = static_cast<uint64_t>((i >> 2) * (BOX_BYTES >> 4) + 2 * (i & 3));
+              umma_ts_f16(o_tm, p_tm + 8 * i, v_desc + adv, idesc, (j > 0 || i != 0) ? 1u : 0u);
+            }
+            umma_commit(&pv_done[x]);
+            umma_commit(&kv_empty[slot]);
           }
-          umma_commit(&kv_empty[slot]);
+          __syncwarp();
           return true;
         };
-        bool ok = mbar_wait(q_full, 0, abort_flag) && issue_qk(0);
-        for (int j = 0; ok && j < n_kv; ++j) {
-          ok = issue_pv(j);
-          if (ok && j + 1 < n_kv) ok = issue_qk(j + 1);
+        // warp 9 issues every Q.K^T (tile 0, tile 1, tile 0, ... through the shared score buffer), warp 10 every P.V
+        if (warp == ISSUER_WARP0) {
+          bool ok = mbar_wait(q_full, 0, abort_flag);
+          for (int j = 0; ok && j < n_kv; ++j) ok = issue_qk(0, j) && issue_qk(1, j);
+        } else {
+          bool ok = true;
+          for (int j = 0; ok && j < n_kv; ++j) ok = issue_pv(0, j) && issue_pv(1, j);
         }
-        if (ok) umma_commit(&o_done[x]);
       }
     }
   } else {
     // ---------------------------------------------------------------- softmax / correction / epilogue
-    reg_alloc_224();
+    reg_alloc_216();
     const int x = warp >> 2;            // query tile
     const int quarter = warp & 3;       // TMEM lanes [32*quarter, +32)
     const int r = quarter * 32 + lane;  // row inside the tile
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t s_tmem = tmem_base + lane_base + x * 128;
-    const uint32_t p_tmem = s_tmem + 64;
+    const uint32_t s_tmem = tmem_base + lane_base;
+    const uint32_t p_tmem = tmem_base + lane_base + 128 + x * 64;
     const uint32_t o_tmem = tmem_base + lane_base + 256 + x * 128;
     const int q_row = q0 + x * 128 + r;
     // 16-bit scores are unscaled: the per-row factor (softmax scale * log2 e) multiplies them here
@@ -220,6 +239,9 @@ attn_fwd_tmem_p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(s_tmem + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&sv[32 * c]));
       tmem_wait_ld();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_free);  // S is in registers: the other tile's Q.K^T may overwrite it
       const int valid = p.Sk - j * 128;  // columns >= valid are padding (only in the last tile)
       if (valid < 128) {
 #pragma unroll
@@ -234,8 +256,12 @@ attn_fwd_tmem_p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const float alpha = ex2(m - m_new);  // m = -inf on the first tile -> 0
       const float off = -m_new;
 
-      // correction: O_X *= alpha when a row of this warp moved its maximum.  S_X(j) complete implies that
-      // P_X(j-1).V_{j-1} has completed (same issuing thread, in order), so O_X is at rest.
+      // P_X and O_X are at rest once P_X(j-1).V_{j-1} has completed (normally long ago)
+      if (j > 0) {
+        if (!mbar_wait(&pv_done[x], (j - 1) & 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+      }
+      // correction: O_X *= alpha when a row of this warp moved its maximum
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
@@ -248,7 +274,7 @@ attn_fwd_tmem_p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
       }
 
-      // p_i = 2^(s_i * cmul - m_new), packed to bf16 pairs: P_X(j) goes back to tensor memory in two halves
+      // p_i = 2^(s_i * cmul - m_new), packed to bf16 pairs, to tensor memory
       float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int hseg = 0; hseg < 2; ++hseg) {
@@ -272,7 +298,7 @@ attn_fwd_tmem_p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       m = m_new;
     }
 
-    if (ok && mbar_wait(&o_done[x], 0, abort_flag)) {
+    if (ok && mbar_wait(&pv_done[x], (n_kv - 1) & 1u, abort_flag)) {
       tc_fence_after_sync();
       const float inv_l = 1.001953125f / l;  // bf16 P was truncated, not rounded: centre the result
       const bool store = q_row < q_stop;
@@ -340,11 +366,12 @@ int launch_attn_fwd_tmem_p(const AttnWorkspace& ws, const AttnParams& p, int64_t
     int rc = make_tma_map(&map_v, ws.vt, 2, 2, dims, strides, box);
     if (rc != DAX_OK) return rc;
   }
-  DAX_CUDA(cudaFuncSetAttribute(attn_fwd_tmem_p_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
   dim3 grid(static_cast<unsigned>(p.n_ranges * p.tiles_per_range), static_cast<unsigned>(BH));
+  DAX_CUDA(cudaFuncSetAttribute(attn_fwd_tmem_p_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
   attn_fwd_tmem_p_kernel<<<grid, THREADS, SMEM_TOTAL, st>>>(map_q, map_k, map_v, p);
   DAX_CUDA(cudaGetLastError());
   return DAX_OK;
 }
 
 }  // namespace dax
+
