@@ -30,6 +30,14 @@ SIGNATURES = {
     "dax_gemm_dequant_ex": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
                                     c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p,
                                     c_int, c_void_p, c_int64, c_void_p, c_void_p]),
+    "dax_gemm_dequant_scatter": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                         POINTER(c_void_p), c_int64, c_int, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                         c_void_p]),
+    "dax_rmsnorm_rope_pack_scatter": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int,
+                                              c_void_p, c_float, c_void_p, c_void_p, c_int64, POINTER(c_void_p), c_int64,
+                                              c_int64, c_int64, c_void_p]),
+    "dax_attn_forward_scatter": (c_int, [POINTER(c_void_p), c_int64, c_int64, c_int, c_int64, c_int64, c_int64, c_int64,
+                                         c_int64, c_int64, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
     "dax_layernorm_modulate_quant": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
                                              c_void_p, c_float, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p]),
     "dax_linear_dynamic_workspace_bytes": (c_size_t, [c_int64, c_int64]),

@@ -31,7 +31,8 @@ from torch import nn
 from ... import ops
 from ...parallel import dist as para_dist
 from ...parallel.patches.wanx2_1_t2v_opt import micro_batch_bounds
-from ...parallel.ulysses import UlyssesExchange, chunk_bounds
+from ...parallel.peer import PeerBuffers, shared_peer_buffers
+from ...parallel.ulysses import UlyssesExchange, _Done, chunk_bounds
 from ...quant.nn.dynamic import Linear as QLinear
 
 HEAD_DIM = 128
@@ -93,7 +94,7 @@ def shared_exchange() -> UlyssesExchange:
 class DAXWanAttnProcessor2_0:
     def __init__(self, sp_size: int = 1, overlap_comm: bool = False, attention_mode: str = "bf16",
                  qkv_chunks: int = 4, o_micro_batches: int = 2, o_split: str = "auto",
-                 sequence_parallel: Optional[bool] = None):
+                 sequence_parallel: Optional[bool] = None, exchange: str = "auto"):
         """``sp_size`` / ``overlap_comm`` as in the reference.  ``attention_mode``: "bf16" (bf16 contractions: the
         mode within rel-L2 1e-2 of fp32 SDPA, default), "sage" (INT8 Q.K^T, FP8 P.V: the reference backend's
         arithmetic) or "int8_bf16".  ``qkv_chunks``: token chunks of the Q/K/V
@@ -102,7 +103,16 @@ class DAXWanAttnProcessor2_0:
         "ranks" (by groups of destination ranks) or "auto" (whichever needs fewer rounds of attention CTAs).
         ``sequence_parallel``: None follows the process-wide parallel state (the reference's behaviour); False
         keeps this processor local even when the state is initialised (an un-sharded layer run next to a sharded
-        one, e.g. to check the sharded result)."""
+        one, e.g. to check the sharded result).
+        ``exchange``: how the two sequence<->head exchanges travel when ``overlap_comm`` is on.  "peer": the producing
+        kernels store straight into the other GPUs' receive buffers over NVLink (peer-mapped symmetric memory) and a
+        device-side barrier replaces the collective: the transfer is part of the kernels, nothing is chunked;
+        "nccl": chunked point-to-point groups on NCCL's stream overlapping the next chunk's kernels; "auto": "peer"
+        where peer-mapped buffers are available, else "nccl".  ``overlap_comm=False`` always takes one synchronous
+        NCCL exchange per direction, as the reference does."""
+        if exchange not in ("auto", "peer", "nccl"):
+            raise ValueError("exchange must be 'auto', 'peer' or 'nccl'")
+        self.exchange = exchange
         self.sequence_parallel = sequence_parallel
         if o_split not in ("auto", "rows", "ranks"):
             raise ValueError("o_split must be 'auto', 'rows' or 'ranks'")
@@ -127,12 +137,16 @@ class DAXWanAttnProcessor2_0:
     @staticmethod
     def _project(lin: nn.Module, x_rows: torch.Tensor, q_pair, *, out: torch.Tensor, ldo: int, col_group: int,
                  group_stride: int, row_sumsq: Optional[torch.Tensor], resid: Optional[torch.Tensor] = None,
-                 gate: Optional[torch.Tensor] = None) -> None:
+                 gate: Optional[torch.Tensor] = None, group_ptrs=None) -> None:
         """``out <- lin(x_rows)`` in the (grouped) layout given by ldo / col_group / group_stride; with
-        ``resid`` the gated residual ``out <- resid + gate * lin(x_rows)`` (fused into the GEMM epilogue)."""
+        ``resid`` the gated residual ``out <- resid + gate * lin(x_rows)`` (fused into the GEMM epilogue); with
+        ``group_ptrs`` (quantised linears only) the column groups go to those addresses instead of ``out``."""
         if isinstance(lin, QLinear):
             lin._check_supported()
             qx, sx = q_pair
+            if group_ptrs is not None:
+                lin.forward_quantized(qx, sx, ldo=ldo, out_col_group=col_group, group_ptrs=group_ptrs)
+                return
             lin.forward_quantized(qx, sx, out=out, ldo=ldo, out_col_group=col_group,
                                   out_group_stride=group_stride, row_sumsq=row_sumsq, resid=resid, gate=gate)
         else:  # float projection: library GEMM, then a strided copy into the layout
@@ -201,6 +215,13 @@ class DAXWanAttnProcessor2_0:
         if rotary_emb is not None:
             cos, sin = _rope_tables(rotary_emb)
             assert cos.shape[0] >= S, f"rotary table has {cos.shape[0]} rows, sequence has {S}"
+
+        if overlap and self.exchange != "nccl":
+            peers = shared_peer_buffers(xchg.group, P, rank)
+            if peers is not None:
+                return self._self_attention_peer(attn, x, cos, sin, prequant, resid, gate, peers)
+            if self.exchange == "peer":
+                raise RuntimeError("exchange='peer' needs torch.distributed._symmetric_memory on CUDA devices")
 
         # exchange layout [P, s, h*d]: slab p = heads of rank p; with P == 1 this is plain [s, D]
         send = [_BUFFERS.get(f"send{i}", (P, s, hd), dt, dev) for i in range(3)]
@@ -307,6 +328,57 @@ class DAXWanAttnProcessor2_0:
                 self._o_project(o_lin, pending.pop(0), out, P, hd, D, resid, gate)
         while pending:
             self._o_project(o_lin, pending.pop(0), out, P, hd, D, resid, gate)
+        return out
+
+    def _self_attention_peer(self, attn, x: torch.Tensor, cos, sin, prequant, resid, gate, peers: PeerBuffers) -> torch.Tensor:
+        """The sequence-parallel block with both exchanges written by the producing kernels themselves into the
+        other ranks' receive buffers (peer mappings): un-chunked projections, one attention launch, two
+        device-side barriers.  Same results as the NCCL paths (the kernels and their order per token are the same)."""
+        s, D = x.shape
+        H = attn.heads
+        dev, dt = x.device, x.dtype
+        P, rank = peers.P, peers.rank
+        h = H // P
+        hd = h * HEAD_DIM
+        S = s * P
+        esz = x.element_size()
+        recv, recv_ptrs = peers.get("qkv_recv", (3, S, hd), dt, dev)      # [tensor, all tokens, my heads]
+        o_recv, o_ptrs = peers.get("o_recv", (P, s, hd), dt, dev)         # slab p = rank p's heads for my tokens
+        n_tiles = 2 * ((D + 255) // 256)
+        lins = (attn.to_q, attn.to_k, attn.to_v)
+        norms = (attn.norm_q, attn.norm_k, None)
+        pairs = ([prequant if isinstance(lin, QLinear) else None for lin in lins] if prequant is not None
+                 else self._quantize_for(lins, x))
+        for i, (lin, norm) in enumerate(zip(lins, norms)):
+            # rank p owns head group p: my rows of tensor i land at rows [rank * s, (rank + 1) * s) of ITS buffer
+            dests = [recv_ptrs[p] + ((i * S + rank * s) * hd) * esz for p in range(P)]
+            plain = norm is None and (i == 2 or cos is None)
+            if plain and isinstance(lin, QLinear):
+                self._project(lin, x, pairs[i], out=None, ldo=hd, col_group=hd, group_stride=0, row_sumsq=None,
+                              group_ptrs=dests)
+                continue
+            tmp = _BUFFERS.get("proj_tmp", (s, D), dt, dev)
+            fused = isinstance(lin, QLinear) and norm is not None
+            ss = _BUFFERS.get("row_sumsq", (s, n_tiles), torch.float32, dev) if fused else None
+            self._project(lin, x, pairs[i], out=tmp, ldo=D, col_group=D, group_stride=0, row_sumsq=ss)
+            rope = i != 2 and cos is not None
+            ops.rmsnorm_rope_pack(tmp, norm_weight=getattr(norm, "weight", None) if norm is not None else None,
+                                  do_norm=norm is not None, eps=getattr(norm, "eps", 1e-6) if norm is not None else 1e-6,
+                                  rope_cos=cos if rope else None, rope_sin=sin if rope else None, token_offset=rank * s,
+                                  row_sumsq=ss, ldo=hd, col_group=hd, group_ptrs=dests)
+        peers.barrier(0)  # every rank's Q, K, V rows have landed in my buffers
+
+        def bhsd(t):
+            return t.view(1, S, h, HEAD_DIM).transpose(1, 2)
+
+        plan = ops.attn_prepare(bhsd(recv[0]), bhsd(recv[1]), bhsd(recv[2]), self.attention_mode,
+                                1.0 / math.sqrt(HEAD_DIM))
+        # query row q belongs to rank q // s: its result goes to slab `rank` of that rank's o_recv
+        o_dests = [o_ptrs[d] + (rank * s * hd) * esz for d in range(P)]
+        ops.attn_forward_scatter(plan, o_dests, rows_per_dest=s, head_stride=HEAD_DIM, token_stride=hd)
+        peers.barrier(1)  # every rank's attention rows for my tokens have landed
+        out = torch.empty((s, D), dtype=dt, device=dev)
+        self._o_project(attn.to_out[0], (_Done(), o_recv, 0, s), out, P, hd, D, resid, gate)
         return out
 
     def _o_project(self, o_lin, item, out: torch.Tensor, P: int, hd: int, D: int, resid=None, gate=None) -> None:

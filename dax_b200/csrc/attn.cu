@@ -464,7 +464,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const float inv_l = (C::EP == 2 ? 1.001953125f : 1.f) / (l + l2);
         const bool store = q_row < q_stop;
         const int b = bh / p.heads, h = bh % p.heads;
-        uint16_t* orow = static_cast<uint16_t*>(p.o) + b * p.o_sb + h * p.o_sh + static_cast<int64_t>(q_row) * p.o_st + half * 64;
+        uint16_t* orow = static_cast<uint16_t*>(p.o) + attn_out_offset(p, b, h, q_row) + half * 64;
         const float* vs = vscale_s + half * 64;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -542,11 +542,11 @@ int launch_fwd(const AttnWorkspace& ws, const AttnParams& p, int64_t BH, cudaStr
 }  // namespace
 }  // namespace dax
 
-extern "C" int dax_attn_forward(void* o, int dtype, int64_t B, int64_t heads, int64_t Sq, int64_t Sk,
-                                int64_t o_strides[3], int64_t q_begin, int64_t q_end, int64_t n_ranges,
-                                int64_t range_stride, int mode, void* workspace, size_t workspace_bytes,
-                                void* stream) {
-  using namespace dax;
+namespace dax {
+namespace {
+int attn_forward_entry(void* o, int dtype, int64_t B, int64_t heads, int64_t Sq, int64_t Sk, const int64_t o_strides[3],
+                       int64_t q_begin, int64_t q_end, int64_t n_ranges, int64_t range_stride, const GroupTable& dest,
+                       int64_t rows_per_dest, int mode, void* workspace, size_t workspace_bytes, void* stream) {
   DAX_REQUIRE(o && workspace && o_strides, DAX_ERR_INVALID, "attn_forward: null pointer");
   DAX_REQUIRE(dtype == DAX_BF16 || dtype == DAX_F16, DAX_ERR_UNSUPPORTED, "attn_forward: dtype %d is not BF16/F16", dtype);
   AttnWorkspace ws;
@@ -558,6 +558,9 @@ extern "C" int dax_attn_forward(void* o, int dtype, int64_t B, int64_t heads, in
                   q_end + (n_ranges - 1) * range_stride <= Sq,
               DAX_ERR_INVALID, "attn_forward: %lld ranges of stride %lld do not fit Sq=%lld", (long long)n_ranges,
               (long long)range_stride, (long long)Sq);
+  DAX_REQUIRE(dest.n == 0 || (B == 1 && rows_per_dest > 0 && static_cast<int64_t>(dest.n) * rows_per_dest >= Sq),
+              DAX_ERR_INVALID, "attn_forward: %d destinations of %lld rows do not cover Sq=%lld (batch must be 1)", dest.n,
+              (long long)rows_per_dest, (long long)Sq);
   if (q_begin == q_end) return DAX_OK;
   DAX_REQUIRE(aligned16(o) && o_strides[0] % 8 == 0 && o_strides[1] % 8 == 0 && o_strides[2] % 8 == 0, DAX_ERR_ALIGN,
               "attn_forward: o must be 16-byte aligned with strides that are multiples of 8 elements");
@@ -574,9 +577,34 @@ extern "C" int dax_attn_forward(void* o, int dtype, int64_t B, int64_t heads, in
   p.n_ranges = static_cast<int>(n_ranges); p.range_stride = static_cast<int>(range_stride);
   p.tiles_per_range = static_cast<int>((q_end - q_begin + 255) / 256);
   p.out_bf16 = dtype == DAX_BF16;
+  p.dest = dest;
+  p.rows_per_dest = static_cast<int>(rows_per_dest > 0 ? rows_per_dest : 1);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (mode == DAX_ATTN_QK_I8_PV_F8) return launch_fwd<DAX_ATTN_QK_I8_PV_F8>(ws, p, B * heads, st);
   if (mode == DAX_ATTN_QK_I8_PV_BF16) return launch_fwd<DAX_ATTN_QK_I8_PV_BF16>(ws, p, B * heads, st);
   return launch_attn_fwd_tmem_p(ws, p, B * heads, st);  // bf16 Q.K^T + bf16 P.V: attn_tmem.cu
 }
+}  // namespace
+}  // namespace dax
 
+extern "C" int dax_attn_forward(void* o, int dtype, int64_t B, int64_t heads, int64_t Sq, int64_t Sk,
+                                int64_t o_strides[3], int64_t q_begin, int64_t q_end, int64_t n_ranges,
+                                int64_t range_stride, int mode, void* workspace, size_t workspace_bytes,
+                                void* stream) {
+  dax::GroupTable none{};
+  return dax::attn_forward_entry(o, dtype, B, heads, Sq, Sk, o_strides, q_begin, q_end, n_ranges, range_stride, none, 0,
+                                 mode, workspace, workspace_bytes, stream);
+}
+
+extern "C" int dax_attn_forward_scatter(void* const* o_dest, int64_t n_dest, int64_t rows_per_dest, int dtype,
+                                        int64_t heads, int64_t Sq, int64_t Sk, int64_t head_stride,
+                                        int64_t token_stride, int64_t q_begin, int64_t q_end, int mode,
+                                        void* workspace, size_t workspace_bytes, void* stream) {
+  dax::GroupTable tab{};
+  void* base = nullptr;
+  int rc = dax::make_group_table(o_dest, n_dest, 2, &tab, &base);
+  if (rc != DAX_OK) return rc;
+  int64_t strides[3] = {0, head_stride, token_stride};
+  return dax::attn_forward_entry(base, dtype, 1, heads, Sq, Sk, strides, q_begin, q_end, 1, 0, tab, rows_per_dest, mode,
+                                 workspace, workspace_bytes, stream);
+}

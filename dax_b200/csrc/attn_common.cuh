@@ -42,7 +42,21 @@ struct AttnParams {
   int q_begin, q_end;      // first query range
   int n_ranges, range_stride, tiles_per_range;
   int out_bf16;
+  // scattered output (dest.n > 0): query row q belongs to destination q / rows_per_dest and is written at
+  // o + dest.off[q / rows_per_dest] + (q % rows_per_dest) * o_st + head * o_sh  (the head->sequence exchange of the
+  // sequence-parallel attention written by the kernel itself, each destination being another GPU's buffer)
+  GroupTable dest;
+  int rows_per_dest;
 };
+
+// Address of output row q_row of (batch b, head h), element units.
+__device__ __forceinline__ int64_t attn_out_offset(const AttnParams& p, int b, int h, int q_row) {
+  if (p.dest.n > 0) {
+    const int d = q_row / p.rows_per_dest;
+    return p.dest.off[d < kMaxGroups ? d : 0] + static_cast<int64_t>(q_row - d * p.rows_per_dest) * p.o_st + h * p.o_sh;
+  }
+  return b * p.o_sb + h * p.o_sh + static_cast<int64_t>(q_row) * p.o_st;
+}
 
 inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 

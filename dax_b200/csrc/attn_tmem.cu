@@ -303,7 +303,7 @@ attn_fwd_tmem_p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const float inv_l = 1.001953125f / l;  // bf16 P was truncated, not rounded: centre the result
       const bool store = q_row < q_stop;
       const int b = bh / p.heads, h = bh % p.heads;
-      uint16_t* orow = static_cast<uint16_t*>(p.o) + b * p.o_sb + h * p.o_sh + static_cast<int64_t>(q_row) * p.o_st;
+      uint16_t* orow = static_cast<uint16_t*>(p.o) + attn_out_offset(p, b, h, q_row);
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t ov[32];

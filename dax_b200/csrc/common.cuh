@@ -48,6 +48,33 @@ inline int dtype_bytes(int dt) {
   }
 }
 
+// ---- scattered column groups ------------------------------------------------------------------
+// Several kernels write a [rows, N] matrix as column groups of `col_group` columns that live in separate slabs:
+// element (t, n) goes to  out + off[n / col_group] + t * ld + (n % col_group)  (element units).  With n == 0 the
+// slabs are equally spaced (off[g] = g * group_stride, any number of groups); with n > 0 the table gives the
+// offset of every slab relative to `out`, which lets a slab sit anywhere in the address space, in particular in
+// the memory of another GPU of the node (peer mapping): that is how the sequence<->head exchange of the
+// sequence-parallel attention is written by the producing kernels themselves.
+constexpr int kMaxGroups = 8;
+struct GroupTable {
+  int64_t off[kMaxGroups];
+  int n;
+};
+
+// Fills `tab` (and the base pointer) from a host array of `n` device pointers; elem_bytes = size of one element.
+inline int make_group_table(void* const* ptrs, int64_t n, int elem_bytes, GroupTable* tab, void** base) {
+  DAX_REQUIRE(ptrs != nullptr && n >= 1 && n <= kMaxGroups, DAX_ERR_INVALID,
+              "scatter: between 1 and %d group pointers are needed (got %lld)", kMaxGroups, (long long)n);
+  for (int64_t g = 0; g < n; ++g) {
+    DAX_REQUIRE(ptrs[g] != nullptr && aligned16(ptrs[g]), DAX_ERR_ALIGN, "scatter: group pointer %lld is null or not 16-byte aligned", (long long)g);
+    tab->off[g] = (reinterpret_cast<intptr_t>(ptrs[g]) - reinterpret_cast<intptr_t>(ptrs[0])) / elem_bytes;
+  }
+  for (int64_t g = n; g < kMaxGroups; ++g) tab->off[g] = 0;
+  tab->n = static_cast<int>(n);
+  *base = ptrs[0];
+  return DAX_OK;
+}
+
 // ---- device status word ---------------------------------------------------------------------
 // Kernels store an error code into this word when a bounded wait gives up.  The word is a
 // file-scope __device__ variable of capi.cu; kernels of other translation units get its address

@@ -39,6 +39,7 @@ struct GemmParams {
   void* acc_dump;
   int* status;
   int64_t M, N, K, ldo, out_col_group, out_group_stride;
+  GroupTable groups;  // n > 0: slab g of the output sits at out + groups.off[g] (scattered, e.g. in peer memory)
   int m_tiles, n_tiles, k_blocks;
   int bias_dtype;
   // optional post-operations on the rounded linear output y (16-bit outputs only):
@@ -285,7 +286,8 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         if (row_ok) {
           const int64_t g = col0 / p.out_col_group;
-          const int64_t off = g * p.out_group_stride + row * p.ldo + (col0 - g * p.out_col_group);
+          const int64_t off = (p.groups.n > 0 ? p.groups.off[g < kMaxGroups ? g : 0] : g * p.out_group_stride) + row * p.ldo +
+                              (col0 - g * p.out_col_group);
           if constexpr (OUT == DAX_F32) {
             float* o = static_cast<float*>(p.out) + off;
 #pragma unroll
@@ -356,12 +358,12 @@ extern "C" int dax_gemm_dequant(const void* qx, int a_dtype, const float* sx, co
                              out_col_group, out_group_stride, row_sumsq, acc_dump, 0, nullptr, 0, nullptr, stream);
 }
 
-extern "C" int dax_gemm_dequant_ex(const void* qx, int a_dtype, const float* sx, const void* qw, int b_dtype,
-                                   const float* sw, const void* bias, int bias_dtype, void* out, int out_dtype,
-                                   int64_t M, int64_t N, int64_t K, int64_t ldo, int64_t out_col_group,
-                                   int64_t out_group_stride, float* row_sumsq, void* acc_dump, int act,
-                                   const void* resid, int64_t ldr, const float* gate, void* stream) {
-  using namespace dax;
+namespace dax {
+namespace {
+int gemm_entry(const void* qx, int a_dtype, const float* sx, const void* qw, int b_dtype, const float* sw,
+               const void* bias, int bias_dtype, void* out, int out_dtype, int64_t M, int64_t N, int64_t K, int64_t ldo,
+               int64_t out_col_group, int64_t out_group_stride, const GroupTable& groups, float* row_sumsq,
+               void* acc_dump, int act, const void* resid, int64_t ldr, const float* gate, void* stream) {
   DAX_REQUIRE(act == 0 || act == 1, DAX_ERR_UNSUPPORTED, "gemm_dequant: unknown activation %d", act);
   DAX_REQUIRE((act == 0 && resid == nullptr) || out_dtype != DAX_F32, DAX_ERR_UNSUPPORTED,
               "gemm_dequant: activation / residual epilogues need a 16-bit output dtype");
@@ -412,6 +414,9 @@ extern "C" int dax_gemm_dequant_ex(const void* qx, int a_dtype, const float* sx,
   p.status = device_status_ptr();
   DAX_REQUIRE(p.status != nullptr, DAX_ERR_CUDA, "gemm_dequant: cannot resolve the device status word");
   p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.out_col_group = out_col_group; p.out_group_stride = out_group_stride;
+  p.groups = groups;
+  DAX_REQUIRE(groups.n == 0 || groups.n == N / out_col_group, DAX_ERR_INVALID,
+              "gemm_dequant: %d group pointers for %lld column groups", groups.n, (long long)(N / out_col_group));
   p.m_tiles = static_cast<int>((M + BM - 1) / BM);
   p.n_tiles = static_cast<int>((N + BN - 1) / BN);
   p.k_blocks = static_cast<int>((K + BKB - 1) / BKB);
@@ -428,4 +433,30 @@ extern "C" int dax_gemm_dequant_ex(const void* qx, int a_dtype, const float* sx,
   }
   const uint32_t idesc = make_idesc(/*c=f32*/ 1, a_dtype == DAX_E5M2 ? 1 : 0, b_dtype == DAX_E5M2 ? 1 : 0, BM, BN);
   return launch_gemm_out<KIND_F8>(out_dtype, map_a, map_b, p, idesc, grid, st);
+}
+}  // namespace
+}  // namespace dax
+
+extern "C" int dax_gemm_dequant_ex(const void* qx, int a_dtype, const float* sx, const void* qw, int b_dtype,
+                                   const float* sw, const void* bias, int bias_dtype, void* out, int out_dtype,
+                                   int64_t M, int64_t N, int64_t K, int64_t ldo, int64_t out_col_group,
+                                   int64_t out_group_stride, float* row_sumsq, void* acc_dump, int act,
+                                   const void* resid, int64_t ldr, const float* gate, void* stream) {
+  dax::GroupTable none{};
+  return dax::gemm_entry(qx, a_dtype, sx, qw, b_dtype, sw, bias, bias_dtype, out, out_dtype, M, N, K, ldo, out_col_group,
+                         out_group_stride, none, row_sumsq, acc_dump, act, resid, ldr, gate, stream);
+}
+
+extern "C" int dax_gemm_dequant_scatter(const void* qx, int a_dtype, const float* sx, const void* qw, int b_dtype,
+                                        const float* sw, const void* bias, int bias_dtype, void* const* group_out,
+                                        int64_t n_groups, int out_dtype, int64_t M, int64_t N, int64_t K, int64_t ldo,
+                                        int64_t out_col_group, void* stream) {
+  dax::GroupTable tab{};
+  void* base = nullptr;
+  const int eb = dax::dtype_bytes(out_dtype);
+  if (eb != 2 && eb != 4) return dax::fail(DAX_ERR_UNSUPPORTED, "gemm_dequant_scatter: out_dtype %d is not BF16/F16/F32", out_dtype);
+  int rc = dax::make_group_table(group_out, n_groups, eb, &tab, &base);
+  if (rc != DAX_OK) return rc;
+  return dax::gemm_entry(qx, a_dtype, sx, qw, b_dtype, sw, bias, bias_dtype, base, out_dtype, M, N, K, ldo, out_col_group, 0,
+                         tab, nullptr, nullptr, 0, nullptr, 0, nullptr, stream);
 }

@@ -42,7 +42,7 @@ rmsnorm_rope_pack_kernel(const uint16_t* __restrict__ x, int64_t s, int64_t D, i
                          const float* __restrict__ row_sumsq, int64_t n_partials, int do_norm,
                          const uint16_t* __restrict__ w, float eps, const float* __restrict__ rope_cos,
                          const float* __restrict__ rope_sin, int64_t token_offset, uint16_t* __restrict__ out,
-                         int64_t ldo, int64_t col_group, int64_t group_stride) {
+                         int64_t ldo, int64_t col_group, int64_t group_stride, const GroupTable tab) {
   __shared__ float red[2][kThreads / 32];
   const int tid = threadIdx.x, lane = tid & 31;
   const int nvec = static_cast<int>(D / 8);
@@ -55,7 +55,7 @@ rmsnorm_rope_pack_kernel(const uint16_t* __restrict__ x, int64_t s, int64_t D, i
   for (int i = 0; i < NV; ++i) {
     const int64_t n = static_cast<int64_t>(tid + i * kThreads) * 8;
     const int64_t g = n / col_group;
-    out_off[i] = g * group_stride + (n - g * col_group);
+    out_off[i] = (tab.n > 0 ? tab.off[g < kMaxGroups ? g : 0] : g * group_stride) + (n - g * col_group);
     if (do_norm && w != nullptr && tid + i * kThreads < nvec) wv[i] = *reinterpret_cast<const V8*>(w + n);
   }
   auto load_row = [&](int64_t row, V8 (&buf)[NV]) {
@@ -168,12 +168,12 @@ int dispatch(int64_t s, int64_t D, cudaStream_t st, Args... args) {
 }  // namespace
 }  // namespace dax
 
-extern "C" int dax_rmsnorm_rope_pack(const void* x, int dtype, int64_t s, int64_t D, int64_t ldx,
-                                     const float* row_sumsq, int64_t n_partials, int do_norm,
-                                     const void* norm_weight, float eps, const float* rope_cos,
-                                     const float* rope_sin, int64_t token_offset, void* out, int64_t ldo,
-                                     int64_t col_group, int64_t group_stride, void* stream) {
-  using namespace dax;
+namespace dax {
+namespace {
+int rope_pack_entry(const void* x, int dtype, int64_t s, int64_t D, int64_t ldx, const float* row_sumsq,
+                    int64_t n_partials, int do_norm, const void* norm_weight, float eps, const float* rope_cos,
+                    const float* rope_sin, int64_t token_offset, void* out, int64_t ldo, int64_t col_group,
+                    int64_t group_stride, const GroupTable& tab, void* stream) {
   DAX_REQUIRE(s >= 0 && D > 0, DAX_ERR_INVALID, "rmsnorm_rope_pack: bad shape s=%lld D=%lld", (long long)s, (long long)D);
   if (s == 0) return DAX_OK;
   DAX_REQUIRE(x && out, DAX_ERR_INVALID, "rmsnorm_rope_pack: null pointer");
@@ -182,6 +182,8 @@ extern "C" int dax_rmsnorm_rope_pack(const void* x, int dtype, int64_t s, int64_
               "rmsnorm_rope_pack: D=%lld must be a multiple of 128 and at most %d", (long long)D, 8 * kThreads * kMaxVec);
   DAX_REQUIRE(col_group > 0 && D % col_group == 0 && col_group % 8 == 0, DAX_ERR_ALIGN,
               "rmsnorm_rope_pack: col_group=%lld must divide D and be a multiple of 8", (long long)col_group);
+  DAX_REQUIRE(tab.n == 0 || tab.n == D / col_group, DAX_ERR_INVALID,
+              "rmsnorm_rope_pack: %d group pointers for %lld column groups", tab.n, (long long)(D / col_group));
   DAX_REQUIRE(ldx % 8 == 0 && ldo % 8 == 0 && group_stride % 8 == 0, DAX_ERR_ALIGN,
               "rmsnorm_rope_pack: ldx, ldo, group_stride must be multiples of 8 elements");
   DAX_REQUIRE(aligned16(x) && aligned16(out) && (norm_weight == nullptr || aligned16(norm_weight)) &&
@@ -196,7 +198,32 @@ extern "C" int dax_rmsnorm_rope_pack(const void* x, int dtype, int64_t s, int64_
   uint16_t* op = static_cast<uint16_t*>(out);
   if (dtype == DAX_BF16)
     return dispatch<true>(s, D, st, xp, s, D, ldx, row_sumsq, n_partials, do_norm, wp, eps, rope_cos, rope_sin, token_offset,
-                          op, ldo, col_group, group_stride);
+                          op, ldo, col_group, group_stride, tab);
   return dispatch<false>(s, D, st, xp, s, D, ldx, row_sumsq, n_partials, do_norm, wp, eps, rope_cos, rope_sin, token_offset,
-                         op, ldo, col_group, group_stride);
+                         op, ldo, col_group, group_stride, tab);
+}
+}  // namespace
+}  // namespace dax
+
+extern "C" int dax_rmsnorm_rope_pack(const void* x, int dtype, int64_t s, int64_t D, int64_t ldx,
+                                     const float* row_sumsq, int64_t n_partials, int do_norm,
+                                     const void* norm_weight, float eps, const float* rope_cos,
+                                     const float* rope_sin, int64_t token_offset, void* out, int64_t ldo,
+                                     int64_t col_group, int64_t group_stride, void* stream) {
+  dax::GroupTable tab{};
+  return dax::rope_pack_entry(x, dtype, s, D, ldx, row_sumsq, n_partials, do_norm, norm_weight, eps, rope_cos, rope_sin,
+                              token_offset, out, ldo, col_group, group_stride, tab, stream);
+}
+
+extern "C" int dax_rmsnorm_rope_pack_scatter(const void* x, int dtype, int64_t s, int64_t D, int64_t ldx,
+                                             const float* row_sumsq, int64_t n_partials, int do_norm,
+                                             const void* norm_weight, float eps, const float* rope_cos,
+                                             const float* rope_sin, int64_t token_offset, void* const* group_out,
+                                             int64_t n_groups, int64_t ldo, int64_t col_group, void* stream) {
+  dax::GroupTable tab{};
+  void* base = nullptr;
+  int rc = dax::make_group_table(group_out, n_groups, 2, &tab, &base);
+  if (rc != DAX_OK) return rc;
+  return dax::rope_pack_entry(x, dtype, s, D, ldx, row_sumsq, n_partials, do_norm, norm_weight, eps, rope_cos, rope_sin,
+                              token_offset, base, ldo, col_group, 0, tab, stream);
 }

@@ -85,6 +85,12 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
 
+def _ptr_array(ptrs):
+    """Host array of device pointers for the ``*_scatter`` entry points."""
+    import ctypes
+    return (ctypes.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
+
+
 def quant_rowwise(x: torch.Tensor, q_dtype: torch.dtype, *, col_group: Optional[int] = None,
                   group_stride: int = 0, rows: Optional[int] = None, cols: Optional[int] = None,
                   ldx: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -116,14 +122,25 @@ def gemm_dequant(qx: torch.Tensor, sx: torch.Tensor, qw: torch.Tensor, sw: torch
                  ldo: Optional[int] = None, out_col_group: Optional[int] = None, out_group_stride: int = 0,
                  row_sumsq: Optional[torch.Tensor] = None, acc_dump: Optional[torch.Tensor] = None,
                  act: Optional[str] = None, resid: Optional[torch.Tensor] = None,
-                 gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 gate: Optional[torch.Tensor] = None, group_ptrs=None) -> Optional[torch.Tensor]:
     """``out = cast((acc(qx @ qw.T) * sx) * sw) + bias`` on the tcgen05 INT8 / FP8 pipe, optionally followed
-    by ``act="gelu_tanh"`` and / or the gated residual ``out = resid + gate * out`` (gate ``[N]`` fp32)."""
+    by ``act="gelu_tanh"`` and / or the gated residual ``out = resid + gate * out`` (gate ``[N]`` fp32).
+    With ``group_ptrs`` (device addresses, one per group of ``out_col_group`` columns, possibly peer mappings of
+    other GPUs' buffers) row ``t`` of group ``g`` is stored at ``group_ptrs[g] + t * ldo``; nothing is returned."""
     _need_cuda(qx, sx, qw, sw, bias, out)
     M, K = qx.shape
     N = qw.shape[0]
     assert qw.shape[1] == K and qx.is_contiguous() and qw.is_contiguous()
     assert sx.numel() == M and sw.numel() == N and sx.dtype == torch.float32 and sw.dtype == torch.float32
+    if group_ptrs is not None:
+        assert out is None and row_sumsq is None and acc_dump is None and act is None and resid is None
+        tok = TRACE.begin("gemm_dequant")
+        check(load().dax_gemm_dequant_scatter(qx.data_ptr(), _dt(qx.dtype), sx.data_ptr(), qw.data_ptr(), _dt(qw.dtype),
+                                              sw.data_ptr(), _ptr(bias), _dt(bias.dtype) if bias is not None else 0,
+                                              _ptr_array(group_ptrs), len(group_ptrs), _dt(out_dtype), M, N, K, ldo,
+                                              out_col_group, _stream()))
+        TRACE.end(tok, (M, N, K))
+        return None
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=qx.device)
         ldo = N
@@ -194,12 +211,16 @@ def rmsnorm_rope_pack(x: torch.Tensor, *, norm_weight: Optional[torch.Tensor], d
                       rope_cos: Optional[torch.Tensor] = None, rope_sin: Optional[torch.Tensor] = None,
                       token_offset: int = 0, row_sumsq: Optional[torch.Tensor] = None,
                       out: Optional[torch.Tensor] = None, ldo: Optional[int] = None,
-                      col_group: Optional[int] = None, group_stride: int = 0) -> torch.Tensor:
-    """RMSNorm over the full row + rotary embedding + write into a (possibly grouped) layout."""
+                      col_group: Optional[int] = None, group_stride: int = 0, group_ptrs=None) -> Optional[torch.Tensor]:
+    """RMSNorm over the full row + rotary embedding + write into a (possibly grouped) layout.  With ``group_ptrs``
+    (one device address per column group, possibly in other GPUs' memory) row ``t`` of group ``g`` goes to
+    ``group_ptrs[g] + t * ldo``."""
     _need_cuda(x, norm_weight, rope_cos, rope_sin, row_sumsq, out)
     s, D = x.shape
     assert x.stride(1) == 1
-    if out is None:
+    if group_ptrs is not None:
+        assert out is None and ldo is not None and col_group is not None
+    elif out is None:
         out = torch.empty((s, D), dtype=x.dtype, device=x.device)
         ldo = D
     if col_group is None:
@@ -220,6 +241,13 @@ def rmsnorm_rope_pack(x: torch.Tensor, *, norm_weight: Optional[torch.Tensor], d
         raise ValueError(f"rmsnorm_rope_pack: row_sumsq must be a contiguous fp32 [>= {s}, n] tensor")
     n_part = row_sumsq.shape[1] if row_sumsq is not None else 0
     tok = TRACE.begin("rmsnorm_rope_pack")
+    if group_ptrs is not None:
+        check(load().dax_rmsnorm_rope_pack_scatter(x.data_ptr(), _dt(x.dtype), s, D, x.stride(0), _ptr(row_sumsq), n_part,
+                                                   1 if do_norm else 0, _ptr(norm_weight), float(eps), _ptr(rope_cos),
+                                                   _ptr(rope_sin), token_offset, _ptr_array(group_ptrs), len(group_ptrs),
+                                                   ldo, col_group, _stream()))
+        TRACE.end(tok, (s, D))
+        return None
     check(load().dax_rmsnorm_rope_pack(x.data_ptr(), _dt(x.dtype), s, D, x.stride(0), _ptr(row_sumsq), n_part,
                                        1 if do_norm else 0, _ptr(norm_weight), float(eps), _ptr(rope_cos),
                                        _ptr(rope_sin), token_offset, out.data_ptr(), ldo, col_group, group_stride,
@@ -296,6 +324,21 @@ def attn_forward(plan: AttentionPlan, out: torch.Tensor, q_begin: int = 0, q_end
                                   plan.workspace.numel(), _stream()))
     TRACE.end(tok, (plan.B, plan.heads, (q_end - q_begin) * n_ranges, plan.Sk))
     return out
+
+
+def attn_forward_scatter(plan: AttentionPlan, dest_ptrs, rows_per_dest: int, head_stride: int, token_stride: int,
+                         q_begin: int = 0, q_end: Optional[int] = None) -> None:
+    """The flash pass (batch 1) with every query row written to the destination that owns it: row ``q`` of head
+    ``h`` goes to ``dest_ptrs[q // rows_per_dest] + (q % rows_per_dest) * token_stride + h * head_stride``
+    (elements of the plan's dtype).  The destinations may be other GPUs' buffers (peer mappings)."""
+    assert plan.B == 1
+    if q_end is None:
+        q_end = plan.Sq
+    tok = TRACE.begin("attn_forward")
+    check(load().dax_attn_forward_scatter(_ptr_array(dest_ptrs), len(dest_ptrs), rows_per_dest, _dt(plan.dtype), plan.heads,
+                                          plan.Sq, plan.Sk, head_stride, token_stride, q_begin, q_end, plan.mode,
+                                          plan.workspace.data_ptr(), plan.workspace.numel(), _stream()))
+    TRACE.end(tok, (plan.B, plan.heads, q_end - q_begin, plan.Sk))
 
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mode: str = "bf16",

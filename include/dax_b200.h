@@ -110,6 +110,18 @@ int dax_gemm_dequant_ex(const void* qx, int a_dtype, const float* sx, const void
                         float* row_sumsq, void* acc_dump, int act, const void* resid, int64_t ldr,
                         const float* gate, void* stream);
 
+/* dax_gemm_dequant whose output column groups sit at unrelated addresses: group g (columns [g * out_col_group,
+ * (g + 1) * out_col_group)) of row t is written at group_out[g] + t * ldo.  group_out is a HOST array of n_groups =
+ * N / out_col_group (at most 8) device pointers, each 16-byte aligned.  A pointer may be the peer mapping of another
+ * GPU's buffer: the V projection of the sequence-parallel block then writes each rank's head group straight into that
+ * rank's receive buffer, which is the sequence->head exchange of
+ * dax/parallel/patches/wanx2_1_t2v_opt/layer.py:181-222 done by the producing kernel (plain stores over NVLink, no
+ * collective call, no pack / unpack copy). */
+int dax_gemm_dequant_scatter(const void* qx, int a_dtype, const float* sx, const void* qw, int b_dtype,
+                             const float* sw, const void* bias, int bias_dtype, void* const* group_out,
+                             int64_t n_groups, int out_dtype, int64_t M, int64_t N, int64_t K, int64_t ldo,
+                             int64_t out_col_group, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * One-call dynamic quantised linear = dax_quant_rowwise followed by dax_gemm_dequant, i.e. the whole of
  * dax.quant.nn.dynamic.Linear.forward (dax/quant/nn/dynamic/linear.py:143-228) for a plain row-major
@@ -169,6 +181,15 @@ int dax_rmsnorm_rope_pack(const void* x, int dtype, int64_t s, int64_t D, int64_
                           const float* rope_cos, const float* rope_sin, int64_t token_offset, void* out,
                           int64_t ldo, int64_t col_group, int64_t group_stride, void* stream);
 
+/* dax_rmsnorm_rope_pack with scattered output groups (see dax_gemm_dequant_scatter): column group g of row t goes
+ * to group_out[g] + t * ldo; the Q and K halves of the same exchange
+ * (dax/adapters/wan/attn_adapter.py:112-130 -> layer.py:181-222). */
+int dax_rmsnorm_rope_pack_scatter(const void* x, int dtype, int64_t s, int64_t D, int64_t ldx, const float* row_sumsq,
+                                  int64_t n_partials, int do_norm, const void* norm_weight, float eps,
+                                  const float* rope_cos, const float* rope_sin, int64_t token_offset,
+                                  void* const* group_out, int64_t n_groups, int64_t ldo, int64_t col_group,
+                                  void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * LayerNorm + adaLN modulation (+ per-token quantisation): the step in front of every quantised linear
  * of a Wan DiT block outside the attention itself (the block is diffusers code called from
@@ -210,6 +231,15 @@ int dax_attn_prepare(const void* q, const void* k, const void* v, int dtype, int
 int dax_attn_forward(void* o, int dtype, int64_t B, int64_t heads, int64_t Sq, int64_t Sk, int64_t o_strides[3],
                      int64_t q_begin, int64_t q_end, int64_t n_ranges, int64_t range_stride, int mode,
                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* dax_attn_forward (batch 1) whose result rows are scattered by destination: query row q belongs to destination
+ * q / rows_per_dest and is written, for head h, at  o_dest[q / rows_per_dest] + (q % rows_per_dest) * token_stride +
+ * h * head_stride  (elements).  o_dest is a HOST array of n_dest (at most 8) device pointers.  With destination d =
+ * rank d's receive buffer (peer mapping) this is the head->sequence exchange in front of the O projection
+ * (dax/adapters/wan/attn_adapter.py:241-300, layer.py:13-29) written by the attention kernel's own epilogue. */
+int dax_attn_forward_scatter(void* const* o_dest, int64_t n_dest, int64_t rows_per_dest, int dtype, int64_t heads,
+                             int64_t Sq, int64_t Sk, int64_t head_stride, int64_t token_stride, int64_t q_begin,
+                             int64_t q_end, int mode, void* workspace, size_t workspace_bytes, void* stream);
 
 #ifdef __cplusplus
 }

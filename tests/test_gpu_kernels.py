@@ -388,3 +388,49 @@ def test_linear_dynamic_matches_two_step(ops, M, N, K):
         assert torch.equal(y, y2)
         if wdt == torch.int8:
             assert torch.equal(y.cpu(), O.linear_int8(x, qw, sw, b, torch.bfloat16))
+
+
+# ---- scattered outputs (the exchange written by the producing kernels) --------------------------------
+def test_scatter_entry_points_match_the_strided_ones(ops):
+    """The *_scatter entry points with every group pointer in a SEPARATE allocation of this GPU (what a peer mapping
+    looks like to the kernel: an unrelated address) give exactly what the strided layouts give."""
+    torch.manual_seed(11)
+    P, s, hd, K = 4, 150, 256, 512
+    N = D = P * hd
+    # GEMM epilogue -> P separate slabs
+    x = torch.randn(s, K).bfloat16()
+    w = (torch.randn(N, K) * 0.02).bfloat16()
+    qw, sw = O.quantize_weight(w, torch.int8)
+    yr, qx, sx, _ = O.linear_int8(x, qw, sw, None, torch.bfloat16, return_parts=True)
+    slabs = [torch.zeros(s + 3, hd, dtype=torch.bfloat16, device=DEV) for _ in range(P)]
+    ops.gemm_dequant(qx.to(DEV), sx.to(DEV), qw.to(DEV), sw.to(DEV).reshape(-1).contiguous(), None, torch.bfloat16,
+                     ldo=hd, out_col_group=hd, group_ptrs=[t[3:].data_ptr() for t in slabs])
+    for g in range(P):
+        assert torch.equal(slabs[g][3:].cpu(), yr[:, g * hd:(g + 1) * hd]) and bool((slabs[g][:3] == 0).all())
+    # RMSNorm + RoPE pack -> P separate slabs
+    grid, H = (2, 5, 15), 8
+    xx = torch.randn(s, D).bfloat16().to(DEV)
+    wn = (1 + 0.1 * torch.randn(D)).bfloat16().to(DEV)
+    fr = O.rope_table(grid)
+    cos = fr.real.float().reshape(s, 64).contiguous().to(DEV)
+    sin = fr.imag.float().reshape(s, 64).contiguous().to(DEV)
+    want = ops.rmsnorm_rope_pack(xx, norm_weight=wn, do_norm=True, rope_cos=cos, rope_sin=sin)
+    slabs = [torch.zeros(s, hd, dtype=torch.bfloat16, device=DEV) for _ in range(P)]
+    ops.rmsnorm_rope_pack(xx, norm_weight=wn, do_norm=True, rope_cos=cos, rope_sin=sin, ldo=hd, col_group=hd,
+                          group_ptrs=[t.data_ptr() for t in slabs])
+    assert torch.equal(torch.cat(slabs, 1), want)
+    # plain scatter copy (no norm, no rotation), one group
+    one = torch.zeros(s, D, dtype=torch.bfloat16, device=DEV)
+    ops.rmsnorm_rope_pack(xx, norm_weight=None, do_norm=False, ldo=D, col_group=D, group_ptrs=[one.data_ptr()])
+    assert torch.equal(one, xx)
+    # attention rows scattered by destination: 3 destinations of 100 rows, each [src slab = 1 of 2, 100, h*d]
+    for mode, tol in (("bf16", 1e-2), ("sage", 5e-2)):
+        q, k, v = qkv(1, 2, 300, 300, seed=3)
+        ref = O.sdpa_fp32(q, k, v)
+        plan = ops.attn_prepare(q.to(DEV), k.to(DEV), v.to(DEV), mode)
+        dests = [torch.full((2, 100, 2 * 128), 7.0, dtype=torch.bfloat16, device=DEV) for _ in range(3)]
+        ops.attn_forward_scatter(plan, [t[1].data_ptr() for t in dests], rows_per_dest=100, head_stride=128, token_stride=256)
+        got = torch.cat([t[1].view(100, 2, 128) for t in dests], 0).permute(1, 0, 2).unsqueeze(0).float().cpu()
+        assert O.rel_l2(got, ref) <= tol and all(bool((t[0] == 7.0).all()) for t in dests)
+    with pytest.raises(ValueError):
+        ops.rmsnorm_rope_pack(xx, norm_weight=None, do_norm=False, ldo=hd, col_group=hd, group_ptrs=[one.data_ptr()] * 3)

@@ -50,14 +50,19 @@ def _worker(rank, world, port, S, D, H, grid, q, mode, linear):
         x, rope = _inputs(S, D, grid)
         s = S // world
         outs = {}
-        for overlap in (False, True, "ranks"):
+        # no overlap (one synchronous NCCL exchange per direction); overlap with the producing kernels storing into the
+        # peers' buffers; overlap over chunked NCCL groups with the O path cut by rows and by destination ranks
+        for overlap in (False, "peer", "nccl_rows", "nccl_ranks"):
             holder = torch.nn.Module()
             holder.blocks = torch.nn.ModuleList([_build(D, H, 3)])
             pipe = _Pipe(holder.to(dev))
             optimize_pipe(pipe, sequence_parallel=True, compile=False, overlap_comm=bool(overlap),
                           int8_linear=linear == "int8", fp8_linear=linear == "fp8", attention_mode=mode)
-            if overlap == "ranks":  # O path cut by groups of destination ranks instead of row slices
-                holder.blocks[0].processor.o_split = "ranks"
+            proc = holder.blocks[0].processor
+            if overlap == "peer":
+                proc.exchange = "peer"
+            elif overlap:
+                proc.exchange, proc.o_split = "nccl", overlap.split("_")[1]
             y = holder.blocks[0](x[:, rank * s:(rank + 1) * s].to(dev), rotary_emb=rope.to(dev))
             torch.cuda.synchronize()
             outs[overlap] = y.float().cpu()
