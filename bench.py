@@ -564,21 +564,23 @@ def main():
             # redirected to this rank's own buffer (same kernels and barriers, no NVLink traffic)
             recv, recv_ptrs = peers.get("qkv_recv", (3, tokens, hd), torch.bfloat16, dev)
             o_recv, o_ptrs = peers.get("o_recv", (world, s, hd), torch.bfloat16, dev)
-            src = torch.zeros((s, DIM), dtype=torch.bfloat16, device=dev)
+            src = torch.zeros((world, s, hd), dtype=torch.bfloat16, device=dev)
             src_o = torch.zeros((tokens, hd), dtype=torch.bfloat16, device=dev)
 
             def exchanges_alone():
                 for _ in range(layers):
-                    for i in range(3):
-                        dests = [recv_ptrs[p] + ((i * tokens + rank * s) * hd) * 2 for p in range(world)]
-                        ops.rmsnorm_rope_pack(src, norm_weight=None, do_norm=False, ldo=hd, col_group=hd, group_ptrs=dests)
-                    for d in range(world):
+                    for i in range(3):  # Q, K, V slabs: copy engines
+                        for dp in range(1, world):
+                            p = (rank + dp) % world
+                            ops.peer_copy(recv_ptrs[p] + ((i * tokens + rank * s) * hd) * 2, src[p])
+                    for dp in range(1, world):  # attention rows: this library's scatter kernel (a plain copy here)
+                        d = (rank + dp) % world
                         ops.rmsnorm_rope_pack(src_o[d * s:(d + 1) * s], norm_weight=None, do_norm=False, ldo=hd, col_group=hd,
                                               group_ptrs=[o_ptrs[d] + rank * s * hd * 2])
                 peers.barrier(0)
             n_groups = 0
-            how_total = ("total = the Q/K/V and O bytes of one step stored into the other ranks' buffers by this library's "
-                         "scatter kernel with nothing else running")
+            how_total = ("total = the Q/K/V slabs (copy engines) and the attention rows (this library's scatter kernel) of one "
+                         "step moved into the other ranks' buffers with nothing else running")
         else:
             xchg.recorded = []
             step(x_dev)
@@ -600,18 +602,34 @@ def main():
         e1.record()
         barrier()
         total_ms = max_over_ranks(e0.elapsed_time(e1)) / 3
-        if peers is not None:
-            peers.local_only = True
-        else:
-            xchg.skip_comm = True
-        step(x_dev)
-        nocomm_ms = timed_steps(3)
-        if peers is not None:
-            peers.local_only = False
-        else:
-            xchg.skip_comm = False
-        step(x_dev)
-        with_ms = timed_steps(3)
+        def set_left_out(flag: bool):
+            if peers is not None:
+                peers.local_only = flag
+            else:
+                xchg.skip_comm = flag
+
+        def leg(left_out: bool):
+            """One warm-up step and three timed steps with the inter-GPU transfers on or left out; also the kernel
+            times and the SM clock during the leg (the step is power-capped, so the clock is part of the result)."""
+            set_left_out(left_out)
+            step(x_dev)
+            clock = ClockSampler(local_rank) if rank == 0 else None
+            if clock:
+                clock.start()
+            ops.TRACE.reset(timing=True)
+            ms = timed_steps(3)
+            mhz = clock.stop()["sm_mhz"] if clock else None
+            kernels = {k: tms / 3 for k, (c, tms, _) in ops.TRACE.summary().items()}
+            ops.TRACE.reset(timing=False)
+            set_left_out(False)
+            return ms, mhz, kernels
+
+        # with / left out / with: the first and the last leg bracket the diagnostic one, so that a drift of the
+        # power-capped clock over the legs shows up instead of being booked as exchange time
+        with_a, mhz_a, with_kernels = leg(False)
+        nocomm_ms, nocomm_mhz, nocomm_kernels = leg(True)
+        with_b, mhz_b, _ = leg(False)
+        with_ms = 0.5 * (with_a + with_b)
         exposed = max(0.0, with_ms - nocomm_ms)
         bytes_out = layers * 4 * s * DIM * 2 * (world - 1) / world
         overlap = {"exchange": "peer_stores" if peers is not None else "nccl_p2p", "total_ms": total_ms, "exposed_ms": exposed,
@@ -619,6 +637,9 @@ def main():
                    "step_ms_with_exchanges": with_ms, "step_ms_exchanges_left_out": nocomm_ms,
                    "bytes_out_per_gpu_per_step": bytes_out, "alone_gbs_per_gpu": bytes_out / (total_ms * 1e-3) / 1e9,
                    "exchange_groups_per_step": n_groups,
+                   "kernel_ms_with_exchanges": with_kernels, "kernel_ms_exchanges_left_out": nocomm_kernels,
+                   "step_ms_with_exchanges_before_and_after": [with_a, with_b],
+                   "sm_mhz_with_exchanges_before_and_after": [mhz_a, mhz_b], "sm_mhz_exchanges_left_out": nocomm_mhz,
                    "how": how_total + "; exposed = step time minus the time of the same schedule with the inter-GPU "
                           "transfers left out (diagnostic leg, its outputs are not used); 3 steps each, max over ranks"}
         assert _lib.device_status() == 0

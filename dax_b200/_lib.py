@@ -22,6 +22,7 @@ SIGNATURES = {
     "dax_version": (c_int, []),
     "dax_last_error": (c_char_p, []),
     "dax_device_status": (c_int, [POINTER(c_int)]),
+    "dax_peer_copy": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
     "dax_quant_rowwise": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int,
                                   c_void_p, c_void_p]),
     "dax_gemm_dequant": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,

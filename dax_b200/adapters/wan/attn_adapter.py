@@ -78,6 +78,17 @@ def _rope_tables(rotary_emb: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return cos, sin
 
 
+_SIDE_STREAMS: Dict[str, torch.cuda.Stream] = {}
+
+
+def _side_stream(device) -> torch.cuda.Stream:
+    """The stream the copy engines' transfers are queued on (one per device)."""
+    st = _SIDE_STREAMS.get(str(device))
+    if st is None:
+        st = _SIDE_STREAMS[str(device)] = torch.cuda.Stream(device=device)
+    return st
+
+
 _EXCHANGES: Dict[int, UlyssesExchange] = {}
 
 
@@ -331,9 +342,11 @@ class DAXWanAttnProcessor2_0:
         return out
 
     def _self_attention_peer(self, attn, x: torch.Tensor, cos, sin, prequant, resid, gate, peers: PeerBuffers) -> torch.Tensor:
-        """The sequence-parallel block with both exchanges written by the producing kernels themselves into the
-        other ranks' receive buffers (peer mappings): un-chunked projections, one attention launch, two
-        device-side barriers.  Same results as the NCCL paths (the kernels and their order per token are the same)."""
+        """The sequence-parallel block over peer-mapped receive buffers, no collective call: the Q / K / V slabs travel
+        by copy engine while the next projection runs, the attention kernel stores every result row straight into the
+        buffer of the rank that owns the token (free inside a compute-bound kernel), two device-side barriers order
+        the ranks.  Un-chunked projections, one attention launch.  Same results as the NCCL paths (the kernels and
+        their order per token are the same)."""
         s, D = x.shape
         H = attn.heads
         dev, dt = x.device, x.dtype
@@ -349,23 +362,37 @@ class DAXWanAttnProcessor2_0:
         norms = (attn.norm_q, attn.norm_k, None)
         pairs = ([prequant if isinstance(lin, QLinear) else None for lin in lins] if prequant is not None
                  else self._quantize_for(lins, x))
-        for i, (lin, norm) in enumerate(zip(lins, norms)):
-            # rank p owns head group p: my rows of tensor i land at rows [rank * s, (rank + 1) * s) of ITS buffer
-            dests = [recv_ptrs[p] + ((i * S + rank * s) * hd) * esz for p in range(P)]
+        # Q, K, V: the producing kernel writes the slab of every OTHER rank into a local send buffer and this rank's own
+        # slab straight into its receive buffer; the copy engines then carry each slab to its owner on a side stream
+        # while the next projection runs on the SMs (a kernel that stored to the peers itself would be held to the
+        # NVLink rate: these kernels are memory-bound or write short row segments).  V goes first, then K, then Q.
+        main = torch.cuda.current_stream()
+        side = _side_stream(dev)
+        send = [_BUFFERS.get(f"send{i}", (P, s, hd), dt, dev) for i in range(3)]
+        for i in (2, 1, 0):
+            lin, norm = lins[i], norms[i]
+            own = recv[i, rank * s:(rank + 1) * s]
+            groups = [own.data_ptr() if p == rank else send[i][p].data_ptr() for p in range(P)]
             plain = norm is None and (i == 2 or cos is None)
             if plain and isinstance(lin, QLinear):
                 self._project(lin, x, pairs[i], out=None, ldo=hd, col_group=hd, group_stride=0, row_sumsq=None,
-                              group_ptrs=dests)
-                continue
-            tmp = _BUFFERS.get("proj_tmp", (s, D), dt, dev)
-            fused = isinstance(lin, QLinear) and norm is not None
-            ss = _BUFFERS.get("row_sumsq", (s, n_tiles), torch.float32, dev) if fused else None
-            self._project(lin, x, pairs[i], out=tmp, ldo=D, col_group=D, group_stride=0, row_sumsq=ss)
-            rope = i != 2 and cos is not None
-            ops.rmsnorm_rope_pack(tmp, norm_weight=getattr(norm, "weight", None) if norm is not None else None,
-                                  do_norm=norm is not None, eps=getattr(norm, "eps", 1e-6) if norm is not None else 1e-6,
-                                  rope_cos=cos if rope else None, rope_sin=sin if rope else None, token_offset=rank * s,
-                                  row_sumsq=ss, ldo=hd, col_group=hd, group_ptrs=dests)
+                              group_ptrs=groups)
+            else:
+                tmp = _BUFFERS.get("proj_tmp", (s, D), dt, dev)
+                fused = isinstance(lin, QLinear) and norm is not None
+                ss = _BUFFERS.get("row_sumsq", (s, n_tiles), torch.float32, dev) if fused else None
+                self._project(lin, x, pairs[i], out=tmp, ldo=D, col_group=D, group_stride=0, row_sumsq=ss)
+                rope = i != 2 and cos is not None
+                ops.rmsnorm_rope_pack(tmp, norm_weight=getattr(norm, "weight", None) if norm is not None else None,
+                                      do_norm=norm is not None, eps=getattr(norm, "eps", 1e-6) if norm is not None else 1e-6,
+                                      rope_cos=cos if rope else None, rope_sin=sin if rope else None, token_offset=rank * s,
+                                      row_sumsq=ss, ldo=hd, col_group=hd, group_ptrs=groups)
+            side.wait_stream(main)
+            for dp in range(1, P):
+                p = (rank + dp) % P  # every rank starts with a different destination
+                # rank p owns head group p: my rows of tensor i land at rows [rank * s, (rank + 1) * s) of ITS buffer
+                ops.peer_copy(recv_ptrs[p] + ((i * S + rank * s) * hd) * esz, send[i][p], stream=side)
+        main.wait_stream(side)
         peers.barrier(0)  # every rank's Q, K, V rows have landed in my buffers
 
         def bhsd(t):

@@ -89,6 +89,13 @@ int dax_version(void) { return 100; }
 
 const char* dax_last_error(void) { return dax::error_buffer(); }
 
+int dax_peer_copy(void* dst, const void* src, size_t bytes, void* stream) {
+  DAX_REQUIRE(dst != nullptr && src != nullptr, DAX_ERR_INVALID, "peer_copy: null pointer");
+  if (bytes == 0) return DAX_OK;
+  DAX_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, static_cast<cudaStream_t>(stream)));
+  return DAX_OK;
+}
+
 int dax_device_status(int* host_status) {
   DAX_REQUIRE(host_status != nullptr, DAX_ERR_INVALID, "host_status is null");
   int* p = dax::device_status_ptr();

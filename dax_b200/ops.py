@@ -91,6 +91,15 @@ def _ptr_array(ptrs):
     return (ctypes.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
 
 
+def peer_copy(dst_ptr: int, src: torch.Tensor, stream: Optional[torch.cuda.Stream] = None) -> None:
+    """Copy the contiguous tensor ``src`` to the device address ``dst_ptr`` (possibly another GPU's buffer) with the
+    copy engines, on ``stream`` (default: the current stream)."""
+    _need_cuda(src)
+    assert src.is_contiguous()
+    st = (stream or torch.cuda.current_stream()).cuda_stream
+    check(load().dax_peer_copy(int(dst_ptr), src.data_ptr(), src.numel() * src.element_size(), st))
+
+
 def quant_rowwise(x: torch.Tensor, q_dtype: torch.dtype, *, col_group: Optional[int] = None,
                   group_stride: int = 0, rows: Optional[int] = None, cols: Optional[int] = None,
                   ldx: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor]:

@@ -232,6 +232,13 @@ int dax_attn_forward(void* o, int dtype, int64_t B, int64_t heads, int64_t Sq, i
                      int64_t q_begin, int64_t q_end, int64_t n_ranges, int64_t range_stride, int mode,
                      void* workspace, size_t workspace_bytes, void* stream);
 
+/* One contiguous device-to-device copy on `stream`, carried out by the GPU's copy engines (no SM is used, so it
+ * runs beside compute kernels).  dst or src may be the peer mapping of another GPU's buffer: this is the transport of
+ * the Q / K / V half of the sequence->head exchange when it overlaps the next projection (the slab a rank produced
+ * for rank p, [s, h*d] contiguous, goes to rows [rank*s, (rank+1)*s) of rank p's receive buffer); it stands where
+ * the reference calls all_to_all_single (dax/parallel/patches/wanx2_1_t2v_opt/layer.py:123-132). */
+int dax_peer_copy(void* dst, const void* src, size_t bytes, void* stream);
+
 /* dax_attn_forward (batch 1) whose result rows are scattered by destination: query row q belongs to destination
  * q / rows_per_dest and is written, for head h, at  o_dest[q / rows_per_dest] + (q % rows_per_dest) * token_stride +
  * h * head_stride  (elements).  o_dest is a HOST array of n_dest (at most 8) device pointers.  With destination d =
