@@ -52,6 +52,8 @@ SIGNATURES = {
     "dax_attn_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64, c_int]),
     "dax_attn_prepare": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, I64x3,
                                  I64x3, I64x3, c_float, c_int, c_void_p, c_size_t, c_void_p]),
+    "dax_attn_prepare_parts": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, I64x3,
+                                       I64x3, I64x3, c_float, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "dax_attn_forward": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, I64x3, c_int64, c_int64,
                                  c_int64, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
 }

@@ -392,14 +392,20 @@ class DAXWanAttnProcessor2_0:
                 p = (rank + dp) % P  # every rank starts with a different destination
                 # rank p owns head group p: my rows of tensor i land at rows [rank * s, (rank + 1) * s) of ITS buffer
                 ops.peer_copy(recv_ptrs[p] + ((i * S + rank * s) * hd) * esz, send[i][p], stream=side)
-        main.wait_stream(side)
-        peers.barrier(0)  # every rank's Q, K, V rows have landed in my buffers
-
+            if i == 1:
+                kv_sent = side.record_event()
         def bhsd(t):
             return t.view(1, S, h, HEAD_DIM).transpose(1, 2)
 
-        plan = ops.attn_prepare(bhsd(recv[0]), bhsd(recv[1]), bhsd(recv[2]), self.attention_mode,
-                                1.0 / math.sqrt(HEAD_DIM))
+        # K and V have landed everywhere well before the last Q rows have: their statistics and operand passes run
+        # under the tail of the Q transfer
+        main.wait_event(kv_sent)
+        peers.barrier(0)  # every rank's K and V rows are in my buffers
+        args = (bhsd(recv[0]), bhsd(recv[1]), bhsd(recv[2]), self.attention_mode, 1.0 / math.sqrt(HEAD_DIM))
+        ops.attn_prepare(*args, parts="kv")
+        main.wait_stream(side)
+        peers.barrier(2)  # ... and every rank's Q rows
+        plan = ops.attn_prepare(*args, parts="q")
         # query row q belongs to rank q // s: its result goes to slab `rank` of that rank's o_recv
         o_dests = [o_ptrs[d] + (rank * s * hd) * esz for d in range(P)]
         ops.attn_forward_scatter(plan, o_dests, rows_per_dest=s, head_stride=HEAD_DIM, token_stride=hd)

@@ -279,7 +279,8 @@ quant_v_kernel(const uint16_t* __restrict__ v, Strides vs, int heads, int64_t Sk
 
 template <bool BF16>
 int run_prepare(const void* q, const void* k, const void* v, int64_t B, int64_t heads, int64_t Sq, int64_t Sk,
-                Strides qs, Strides ks, Strides vs, float sm_scale, int mode, const AttnWorkspace& ws, cudaStream_t st) {
+                Strides qs, Strides ks, Strides vs, float sm_scale, int mode, int parts, const AttnWorkspace& ws,
+                cudaStream_t st) {
   const int64_t BH = B * heads;
   const uint16_t* qp = static_cast<const uint16_t*>(q);
   const uint16_t* kp = static_cast<const uint16_t*>(k);
@@ -287,18 +288,19 @@ int run_prepare(const void* q, const void* k, const void* v, int64_t B, int64_t 
   const bool qk_i8 = attn_qk_bytes(mode) == 1, v_f8 = attn_pv_bytes(mode) == 1;
   const float cscale = sm_scale * 1.4426950408889634f;
   const unsigned bh = static_cast<unsigned>(BH);
-  colstats_kernel<BF16><<<dim3(static_cast<unsigned>(ws.chunks), bh), 256, 0, st>>>(kp, vp, ks, vs, static_cast<int>(heads), Sk, ws.part, ws.chunks);
-  colstats_fin_kernel<<<bh, 128, 0, st>>>(ws.part, ws.chunks, Sk, v_f8 ? 1 : 0, ws.k_mean, ws.v_scale);
   const dim3 gq(static_cast<unsigned>((ws.Sq_pad + 63) / 64), bh), gk(static_cast<unsigned>(ws.Sk_pad / 128), bh);
-  if (qk_i8) {
-    quant_q_kernel<BF16, true><<<gq, 256, 0, st>>>(qp, qs, static_cast<int>(heads), Sq, ws.Sq_pad, cscale, ws.q, ws.q_scale);
-    quant_k_kernel<BF16, true><<<gk, 256, 0, st>>>(kp, ks, static_cast<int>(heads), Sk, ws.Sk_pad, ws.k_mean, ws.k, ws.k_scale);
-  } else {
-    quant_q_kernel<BF16, false><<<gq, 256, 0, st>>>(qp, qs, static_cast<int>(heads), Sq, ws.Sq_pad, cscale, ws.q, ws.q_scale);
-    quant_k_kernel<BF16, false><<<gk, 256, 0, st>>>(kp, ks, static_cast<int>(heads), Sk, ws.Sk_pad, ws.k_mean, ws.k, ws.k_scale);
+  if (parts & DAX_ATTN_PREPARE_KV) {
+    colstats_kernel<BF16><<<dim3(static_cast<unsigned>(ws.chunks), bh), 256, 0, st>>>(kp, vp, ks, vs, static_cast<int>(heads), Sk, ws.part, ws.chunks);
+    colstats_fin_kernel<<<bh, 128, 0, st>>>(ws.part, ws.chunks, Sk, v_f8 ? 1 : 0, ws.k_mean, ws.v_scale);
+    if (qk_i8) quant_k_kernel<BF16, true><<<gk, 256, 0, st>>>(kp, ks, static_cast<int>(heads), Sk, ws.Sk_pad, ws.k_mean, ws.k, ws.k_scale);
+    else quant_k_kernel<BF16, false><<<gk, 256, 0, st>>>(kp, ks, static_cast<int>(heads), Sk, ws.Sk_pad, ws.k_mean, ws.k, ws.k_scale);
+    if (v_f8) quant_v_kernel<BF16, true><<<gk, 256, 0, st>>>(vp, vs, static_cast<int>(heads), Sk, ws.Sk_pad, ws.v_scale, ws.vt);
+    else quant_v_kernel<BF16, false><<<gk, 256, 0, st>>>(vp, vs, static_cast<int>(heads), Sk, ws.Sk_pad, ws.v_scale, ws.vt);
   }
-  if (v_f8) quant_v_kernel<BF16, true><<<gk, 256, 0, st>>>(vp, vs, static_cast<int>(heads), Sk, ws.Sk_pad, ws.v_scale, ws.vt);
-  else quant_v_kernel<BF16, false><<<gk, 256, 0, st>>>(vp, vs, static_cast<int>(heads), Sk, ws.Sk_pad, ws.v_scale, ws.vt);
+  if (parts & DAX_ATTN_PREPARE_Q) {
+    if (qk_i8) quant_q_kernel<BF16, true><<<gq, 256, 0, st>>>(qp, qs, static_cast<int>(heads), Sq, ws.Sq_pad, cscale, ws.q, ws.q_scale);
+    else quant_q_kernel<BF16, false><<<gq, 256, 0, st>>>(qp, qs, static_cast<int>(heads), Sq, ws.Sq_pad, cscale, ws.q, ws.q_scale);
+  }
   DAX_CUDA(cudaGetLastError());
   return DAX_OK;
 }
@@ -314,11 +316,12 @@ extern "C" size_t dax_attn_workspace_bytes(int64_t B, int64_t heads, int64_t Sq,
   return ws.bytes;
 }
 
-extern "C" int dax_attn_prepare(const void* q, const void* k, const void* v, int dtype, int64_t B, int64_t heads,
-                                int64_t Sq, int64_t Sk, int64_t q_strides[3], int64_t k_strides[3],
-                                int64_t v_strides[3], float sm_scale, int mode, void* workspace,
-                                size_t workspace_bytes, void* stream) {
+extern "C" int dax_attn_prepare_parts(const void* q, const void* k, const void* v, int dtype, int64_t B, int64_t heads,
+                                      int64_t Sq, int64_t Sk, int64_t q_strides[3], int64_t k_strides[3],
+                                      int64_t v_strides[3], float sm_scale, int mode, int parts, void* workspace,
+                                      size_t workspace_bytes, void* stream) {
   using namespace dax;
+  DAX_REQUIRE(parts >= 1 && parts <= 3, DAX_ERR_INVALID, "attn_prepare: parts must be a combination of KV (1) and Q (2)");
   DAX_REQUIRE(q && k && v && workspace && q_strides && k_strides && v_strides, DAX_ERR_INVALID, "attn_prepare: null pointer");
   DAX_REQUIRE(dtype == DAX_BF16 || dtype == DAX_F16, DAX_ERR_UNSUPPORTED, "attn_prepare: dtype %d is not BF16/F16", dtype);
   AttnWorkspace ws;
@@ -331,6 +334,14 @@ extern "C" int dax_attn_prepare(const void* q, const void* k, const void* v, int
   const Strides ks{k_strides[0], k_strides[1], k_strides[2]};
   const Strides vs{v_strides[0], v_strides[1], v_strides[2]};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == DAX_BF16) return run_prepare<true>(q, k, v, B, heads, Sq, Sk, qs, ks, vs, sm_scale, mode, ws, st);
-  return run_prepare<false>(q, k, v, B, heads, Sq, Sk, qs, ks, vs, sm_scale, mode, ws, st);
+  if (dtype == DAX_BF16) return run_prepare<true>(q, k, v, B, heads, Sq, Sk, qs, ks, vs, sm_scale, mode, parts, ws, st);
+  return run_prepare<false>(q, k, v, B, heads, Sq, Sk, qs, ks, vs, sm_scale, mode, parts, ws, st);
+}
+
+extern "C" int dax_attn_prepare(const void* q, const void* k, const void* v, int dtype, int64_t B, int64_t heads,
+                                int64_t Sq, int64_t Sk, int64_t q_strides[3], int64_t k_strides[3],
+                                int64_t v_strides[3], float sm_scale, int mode, void* workspace,
+                                size_t workspace_bytes, void* stream) {
+  return dax_attn_prepare_parts(q, k, v, dtype, B, heads, Sq, Sk, q_strides, k_strides, v_strides, sm_scale, mode,
+                                DAX_ATTN_PREPARE_KV | DAX_ATTN_PREPARE_Q, workspace, workspace_bytes, stream);
 }

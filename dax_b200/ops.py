@@ -300,8 +300,10 @@ def attn_workspace(B: int, heads: int, Sq: int, Sk: int, mode: int, device) -> t
 
 
 def attn_prepare(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mode: str = "bf16",
-                 sm_scale: Optional[float] = None) -> AttentionPlan:
-    """q, k, v: ``[B, heads, S, 128]`` views (any batch/head/token strides) of bf16 or fp16."""
+                 sm_scale: Optional[float] = None, parts: str = "all") -> AttentionPlan:
+    """q, k, v: ``[B, heads, S, 128]`` views (any batch/head/token strides) of bf16 or fp16.  ``parts``: "all", or
+    "kv" (statistics, K and V operands) and "q" (Q operands) as two calls on the same shape, for callers whose K and
+    V are complete before Q is."""
     _need_cuda(q, k, v)
     B, heads, Sq, d = q.shape
     Sk = k.shape[2]
@@ -311,9 +313,10 @@ def attn_prepare(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mode: str = 
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(d)
     tok = TRACE.begin("attn_prepare")
-    check(load().dax_attn_prepare(q.data_ptr(), k.data_ptr(), v.data_ptr(), _dt(q.dtype), B, heads, Sq, Sk,
-                                  _bhsd_strides(q), _bhsd_strides(k), _bhsd_strides(v), float(sm_scale), m,
-                                  ws.data_ptr(), ws.numel(), _stream()))
+    TRACE.launches -= {"all": 0, "kv": 1, "q": 4}[parts]  # five kernels in all: four on the K / V side, one for Q
+    check(load().dax_attn_prepare_parts(q.data_ptr(), k.data_ptr(), v.data_ptr(), _dt(q.dtype), B, heads, Sq, Sk,
+                                        _bhsd_strides(q), _bhsd_strides(k), _bhsd_strides(v), float(sm_scale), m,
+                                        {"all": 3, "kv": 1, "q": 2}[parts], ws.data_ptr(), ws.numel(), _stream()))
     TRACE.end(tok, (B, heads, Sq, Sk))
     return AttentionPlan(B, heads, Sq, Sk, m, ws, q.dtype)
 

@@ -228,6 +228,16 @@ int dax_attn_prepare(const void* q, const void* k, const void* v, int dtype, int
                      int64_t Sq, int64_t Sk, int64_t q_strides[3], int64_t k_strides[3], int64_t v_strides[3],
                      float sm_scale, int mode, void* workspace, size_t workspace_bytes, void* stream);
 
+/* dax_attn_prepare in two parts, for callers whose K and V are complete before Q is (the sequence-parallel block:
+ * the K / V statistics and operand passes run while the last Q rows are still in flight between the GPUs):
+ * DAX_ATTN_PREPARE_KV = statistics + K + V operands, DAX_ATTN_PREPARE_Q = Q operands; q may be NULL-free but is not
+ * read by the KV part, k and v are not read by the Q part. */
+#define DAX_ATTN_PREPARE_KV 1
+#define DAX_ATTN_PREPARE_Q 2
+int dax_attn_prepare_parts(const void* q, const void* k, const void* v, int dtype, int64_t B, int64_t heads,
+                           int64_t Sq, int64_t Sk, int64_t q_strides[3], int64_t k_strides[3], int64_t v_strides[3],
+                           float sm_scale, int mode, int parts, void* workspace, size_t workspace_bytes, void* stream);
+
 int dax_attn_forward(void* o, int dtype, int64_t B, int64_t heads, int64_t Sq, int64_t Sk, int64_t o_strides[3],
                      int64_t q_begin, int64_t q_end, int64_t n_ranges, int64_t range_stride, int mode,
                      void* workspace, size_t workspace_bytes, void* stream);
