@@ -2,9 +2,10 @@
 // attention: the normalised, modulated activations feed a quantised linear, so the kernel can emit the
 // INT8 / FP8 codes and scales directly and the separate quantiser pass (and its HBM round trip) goes away.
 //
-// HBM-bound: 2 bytes read per element, 2 written (bf16 output) and/or 1 written (codes).  CTAs stride over
-// the token rows; a row lives in registers (128-bit loads) and the next row's loads are already in flight;
-// mean and centred variance are two CTA reductions in fp32, the absmax of the rounded outputs a third.
+// HBM-bound: 2 bytes read per element, 2 written (bf16 output) and/or 1 written (codes).  One WARP owns a token
+// row: the row lives in the warp's registers (128-bit loads, all issued before the first use), mean, centred
+// variance and the absmax of the rounded outputs are warp shuffles, so no row ever waits at a CTA barrier and the
+// eight warps of a CTA (and the CTAs sharing an SM) hide one another's memory latency.
 //   y = round_dtype( LN(x) [* w + b] [* (1 + scale) + shift] )          LN: eps inside the square root
 //   (q, s) = dynamic per-token quantisation of y, arithmetic of quant_common.cuh
 #include <algorithm>
@@ -14,8 +15,7 @@
 namespace dax {
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kMaxVec = 4;  // rows up to 8192 elements
+constexpr int kMaxVec = 32;  // 16-byte vectors per lane: rows up to 32 * 32 * 8 = 8192 elements
 
 struct alignas(16) V8 { uint32_t w[4]; };  // eight 16-bit elements, two per word
 
@@ -28,37 +28,29 @@ template <bool BF16> __device__ __forceinline__ uint16_t from_f(float f) {
   else return __half_as_ushort(__float2half_rn(f));
 }
 
-// CTA-wide reductions through one of six shared buffers (three reductions per row, two rows' worth): a buffer
-// is rewritten two rows later, with three barriers in between, so one barrier per reduction is enough.
-__device__ __forceinline__ float block_sum(float v, float* red) {
+__device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
-  __syncthreads();
-  float t = 0.f;
-#pragma unroll
-  for (int k = 0; k < kThreads / 32; ++k) t += red[k];
-  return t;
+  return v;
 }
-__device__ __forceinline__ float block_max(float v, float* red) {
+__device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
-  __syncthreads();
-  float t = red[0];
-#pragma unroll
-  for (int k = 1; k < kThreads / 32; ++k) t = fmaxf(t, red[k]);
-  return t;
+  return v;
 }
 
-// QDT < 0: no quantised output.  NV = 16-byte vectors per thread (rows of up to NV * 2048 elements).
+// QDT < 0: no quantised output.  NV = 16-byte vectors per lane (rows of up to NV * 256 elements); vector i of lane l
+// covers elements [8 (l + 32 i), +8), so a warp's loads and stores are contiguous 512-byte runs.
+// Long rows (more than 12 vectors = 48 packed registers per lane) run with 4 warps per CTA and three CTAs per SM so
+// that the row and the pass temporaries fit the register budget without spilling; shorter rows with 8 warps.
+template <int NV> struct LnThreads { static constexpr int value = NV <= 12 ? 256 : 128; };
+
 template <bool BF16, int QDT, int NV>
-__global__ void __launch_bounds__(kThreads, NV <= 3 ? 3 : 2)
+__global__ void __launch_bounds__(LnThreads<NV>::value, NV <= 8 ? 3 : (NV <= 12 ? 2 : 3))
 ln_modulate_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D, int64_t ldx, const float* __restrict__ w,
                          const float* __restrict__ b, const float* __restrict__ shift,
                          const float* __restrict__ scale, float eps, uint16_t* __restrict__ y, int64_t ldy,
                          uint8_t* __restrict__ q, float* __restrict__ qscale) {
-  __shared__ float red[6][kThreads / 32];
   // The per-column vectors (fp32) are four times the bytes of a bf16 row: they are staged in shared memory once
   // per CTA, as mul0/add0 (LayerNorm weight and bias) and mul1/add1 (1 + scale, shift), and read from there
   // for every row.
@@ -67,7 +59,8 @@ ln_modulate_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D
   float* add0 = mul0 + (w != nullptr ? D : 0);
   float* mul1 = add0 + (w != nullptr ? D : 0);
   float* add1 = mul1 + (scale != nullptr ? D : 0);
-  const int tid = threadIdx.x;
+  constexpr int kThreads = LnThreads<NV>::value, kWarps = kThreads / 32;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nvec = static_cast<int>(D / 8);
   for (int64_t n = tid; n < D; n += kThreads) {
     if (w != nullptr) {
@@ -80,24 +73,17 @@ ln_modulate_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D
     }
   }
   __syncthreads();
-  V8 raw[NV], nxt[NV];
-  auto load_row = [&](int64_t row, V8 (&buf)[NV]) {
+  const float inv_d = 1.f / static_cast<float>(D);
+  for (int64_t t = static_cast<int64_t>(blockIdx.x) * kWarps + warp; t < rows; t += static_cast<int64_t>(gridDim.x) * kWarps) {
+    V8 raw[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i)
-      if (tid + i * kThreads < nvec) buf[i] = *reinterpret_cast<const V8*>(x + row * ldx + static_cast<int64_t>(tid + i * kThreads) * 8);
-  };
-  int64_t t = blockIdx.x;
-  if (t < rows) load_row(t, raw);
-  // CTAs stride over the rows; the next row's loads are issued before this row's three reductions
-  for (int it = 0; t < rows; t += gridDim.x, ++it) {
-    if (t + gridDim.x < rows) load_row(t + gridDim.x, nxt);
-    float* rbuf = red[(it & 1) * 3];
-    // The row stays packed (16-bit) in registers and is widened again in each pass: a third of the registers
-    // of an fp32 copy, which is what lets four CTAs share an SM.
+      if (lane + 32 * i < nvec) raw[i] = *reinterpret_cast<const V8*>(x + t * ldx + static_cast<int64_t>(lane + 32 * i) * 8);
+    // The row stays packed (16-bit) in registers and is widened again in each pass.
     float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i)
-      if (tid + i * kThreads < nvec) {
+      if (lane + 32 * i < nvec) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           float lo, hi;
@@ -106,11 +92,11 @@ ln_modulate_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D
           sum += hi;
         }
       }
-    const float mean = block_sum(sum, rbuf) / static_cast<float>(D);
+    const float mean = warp_sum(sum) * inv_d;
     float sq = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i)
-      if (tid + i * kThreads < nvec) {
+      if (lane + 32 * i < nvec) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           float lo, hi;
@@ -121,12 +107,12 @@ ln_modulate_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D
           sq = fmaf(hi, hi, sq);
         }
       }
-    const float rstd = rsqrtf(block_sum(sq, rbuf + kThreads / 32) / static_cast<float>(D) + eps);
+    const float rstd = rsqrtf(warp_sum(sq) * inv_d + eps);
     uint32_t amax2 = 0u;
 #pragma unroll
     for (int i = 0; i < NV; ++i)
-      if (tid + i * kThreads < nvec) {
-        const int64_t n = static_cast<int64_t>(tid + i * kThreads) * 8;
+      if (lane + 32 * i < nvec) {
+        const int64_t n = static_cast<int64_t>(lane + 32 * i) * 8;
         float m0[8], a0[8], m1[8], a1[8];
         if (w != nullptr) {
           *reinterpret_cast<float4*>(&m0[0]) = *reinterpret_cast<const float4*>(mul0 + n);
@@ -160,37 +146,37 @@ ln_modulate_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D
     if constexpr (QDT >= 0) {
       float alo, ahi;
       unpack2<BF16>(amax2, alo, ahi);
-      const float amax = block_max(fmaxf(alo, ahi), rbuf + 2 * (kThreads / 32));
+      const float amax = warp_max(fmaxf(alo, ahi));
       const float s = quant_scale<QDT>(amax, [](float v) { return to_f<BF16>(from_f<BF16>(v)); });
       const float inv = __fdiv_rn(1.0f, s);
-      if (tid == 0) qscale[t] = s;
+      if (lane == 0) qscale[t] = s;
 #pragma unroll
       for (int i = 0; i < NV; ++i)
-        if (tid + i * kThreads < nvec) {
+        if (lane + 32 * i < nvec) {
           float f[8];
 #pragma unroll
           for (int k = 0; k < 4; ++k) unpack2<BF16>(raw[i].w[k], f[2 * k], f[2 * k + 1]);
           const uint32_t w0 = quant_four<QDT>(f[0], f[1], f[2], f[3], s, inv);
           const uint32_t w1 = quant_four<QDT>(f[4], f[5], f[6], f[7], s, inv);
-          *reinterpret_cast<uint2*>(q + t * D + static_cast<int64_t>(tid + i * kThreads) * 8) = make_uint2(w0, w1);
+          *reinterpret_cast<uint2*>(q + t * D + static_cast<int64_t>(lane + 32 * i) * 8) = make_uint2(w0, w1);
         }
     }
-#pragma unroll
-    for (int i = 0; i < NV; ++i) raw[i] = nxt[i];
   }
 }
 
 template <bool BF16, int QDT, int NV>
 int launch(int64_t s, cudaStream_t st, const uint16_t* x, int64_t D, int64_t ldx, const float* w, const float* b,
            const float* shift, const float* scale, float eps, uint16_t* y, int64_t ldy, uint8_t* q, float* qscale) {
-  // as many CTAs as fit on the GPU at once; each strides over the rows
+  // as many CTAs as fit on the GPU at once; each warp strides over the rows
+  constexpr int kThreads = LnThreads<NV>::value, kWarps = kThreads / 32;
   int per_sm = 0;
   const size_t smem = static_cast<size_t>(D) * sizeof(float) * ((w != nullptr ? 2 : 0) + (scale != nullptr ? 2 : 0));
   if (smem > 48 * 1024)
     DAX_CUDA(cudaFuncSetAttribute(ln_modulate_quant_kernel<BF16, QDT, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   static_cast<int>(smem)));
   DAX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ln_modulate_quant_kernel<BF16, QDT, NV>, kThreads, smem));
-  const unsigned grid = static_cast<unsigned>(std::min<int64_t>(s, static_cast<int64_t>(sm_count()) * std::max(per_sm, 1)));
+  const int64_t want = (s + kWarps - 1) / kWarps;
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>(want, static_cast<int64_t>(sm_count()) * std::max(per_sm, 1)));
   ln_modulate_quant_kernel<BF16, QDT, NV><<<grid, kThreads, smem, st>>>(x, s, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
   DAX_CUDA(cudaGetLastError());
   return DAX_OK;
@@ -199,10 +185,18 @@ int launch(int64_t s, cudaStream_t st, const uint16_t* x, int64_t D, int64_t ldx
 template <bool BF16, int QDT>
 int dispatch_nv(int64_t s, cudaStream_t st, const uint16_t* x, int64_t D, int64_t ldx, const float* w, const float* b,
                 const float* shift, const float* scale, float eps, uint16_t* y, int64_t ldy, uint8_t* q, float* qscale) {
-  const int64_t nv = (D / 8 + kThreads - 1) / kThreads;
-  if (nv <= 1) return launch<BF16, QDT, 1>(s, st, x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
-  if (nv <= 2) return launch<BF16, QDT, 2>(s, st, x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
-  if (nv <= 3) return launch<BF16, QDT, 3>(s, st, x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
+  const int64_t nv = (D / 8 + 31) / 32;
+#define DAX_LN_CASE(N) if (nv <= N) return launch<BF16, QDT, N>(s, st, x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale)
+  DAX_LN_CASE(1);
+  DAX_LN_CASE(2);
+  DAX_LN_CASE(4);
+  DAX_LN_CASE(6);
+  DAX_LN_CASE(8);
+  DAX_LN_CASE(12);
+  DAX_LN_CASE(16);
+  DAX_LN_CASE(20);
+  DAX_LN_CASE(24);
+#undef DAX_LN_CASE
   return launch<BF16, QDT, kMaxVec>(s, st, x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
 }
 
@@ -229,8 +223,8 @@ extern "C" int dax_layernorm_modulate_quant(const void* x, int dtype, int64_t s,
   if (s == 0) return DAX_OK;
   DAX_REQUIRE(x != nullptr && (y != nullptr || q != nullptr), DAX_ERR_INVALID, "layernorm_modulate_quant: null pointer");
   DAX_REQUIRE(dtype == DAX_BF16 || dtype == DAX_F16, DAX_ERR_UNSUPPORTED, "layernorm_modulate_quant: dtype %d is not BF16/F16", dtype);
-  DAX_REQUIRE(D % 8 == 0 && D <= 8 * kThreads * kMaxVec, DAX_ERR_UNSUPPORTED,
-              "layernorm_modulate_quant: D=%lld must be a multiple of 8 and at most %d", (long long)D, 8 * kThreads * kMaxVec);
+  DAX_REQUIRE(D % 8 == 0 && D <= 8 * 32 * kMaxVec, DAX_ERR_UNSUPPORTED,
+              "layernorm_modulate_quant: D=%lld must be a multiple of 8 and at most %d", (long long)D, 8 * 32 * kMaxVec);
   DAX_REQUIRE((shift == nullptr) == (scale == nullptr), DAX_ERR_INVALID, "layernorm_modulate_quant: shift and scale come together");
   DAX_REQUIRE(ln_bias == nullptr || ln_weight != nullptr, DAX_ERR_INVALID, "layernorm_modulate_quant: bias needs weight");
   DAX_REQUIRE(q == nullptr || qscale != nullptr, DAX_ERR_INVALID, "layernorm_modulate_quant: q needs qscale");
