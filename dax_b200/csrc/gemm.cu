@@ -392,6 +392,8 @@ int gemm_entry(const void* qx, int a_dtype, const float* sx, const void* qw, int
   DAX_REQUIRE(aligned16(qx) && aligned16(qw) && aligned16(out), DAX_ERR_ALIGN,
               "gemm_dequant: qx, qw and out must be 16-byte aligned");
   DAX_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), DAX_ERR_UNSUPPORTED, "gemm_dequant: size overflow");
+  DAX_REQUIRE(groups.n == 0 || groups.n == N / out_col_group, DAX_ERR_INVALID,
+              "gemm_dequant: %d group pointers for %lld column groups", groups.n, (long long)(N / out_col_group));
 
   CUtensorMap map_a, map_b;
   {
@@ -415,8 +417,6 @@ int gemm_entry(const void* qx, int a_dtype, const float* sx, const void* qw, int
   DAX_REQUIRE(p.status != nullptr, DAX_ERR_CUDA, "gemm_dequant: cannot resolve the device status word");
   p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.out_col_group = out_col_group; p.out_group_stride = out_group_stride;
   p.groups = groups;
-  DAX_REQUIRE(groups.n == 0 || groups.n == N / out_col_group, DAX_ERR_INVALID,
-              "gemm_dequant: %d group pointers for %lld column groups", groups.n, (long long)(N / out_col_group));
   p.m_tiles = static_cast<int>((M + BM - 1) / BM);
   p.n_tiles = static_cast<int>((N + BN - 1) / BN);
   p.k_blocks = static_cast<int>((K + BKB - 1) / BKB);

@@ -209,3 +209,32 @@ def test_unknown_cache_strategy_disables_teacache():
 
     t = replace_transformer(T(), cache_strategy="something_else")
     assert type(t).enable_teacache is False
+
+
+def test_scatter_entry_points_validate_their_pointer_tables(built_library):
+    """The *_scatter entry points reject a bad table of group pointers before anything is launched."""
+    lib = _lib.load()
+    one = ctypes.c_void_p(4096)
+
+    def table(*vals):
+        return (ctypes.c_void_p * len(vals))(*vals)
+
+    args = (one, _lib.DAX_BF16, 4, 512, 512, None, 0, 0, None, ctypes.c_float(1e-6), None, None, 0)
+    # nine groups: more than the table holds
+    assert lib.dax_rmsnorm_rope_pack_scatter(*args, table(*([4096] * 9)), 9, 64, 64, None) == _lib.DAX_ERR_INVALID
+    assert b"group pointers" in lib.dax_last_error()
+    # a pointer that is not 16-byte aligned, a null entry
+    assert lib.dax_rmsnorm_rope_pack_scatter(*args, table(4096, 4104), 2, 256, 256, None) == _lib.DAX_ERR_ALIGN
+    assert lib.dax_rmsnorm_rope_pack_scatter(*args, table(4096, None), 2, 256, 256, None) == _lib.DAX_ERR_ALIGN
+    # number of pointers must equal the number of column groups
+    assert lib.dax_rmsnorm_rope_pack_scatter(*args, table(4096, 8192, 12288), 3, 256, 256, None) == _lib.DAX_ERR_INVALID
+    rc = lib.dax_gemm_dequant_scatter(one, _lib.DAX_I8, one, one, _lib.DAX_I8, one, None, 0, table(4096, 8192, 12288), 3,
+                                      _lib.DAX_BF16, 32, 512, 64, 256, 256, None)
+    assert rc == _lib.DAX_ERR_INVALID
+    # attention rows: destinations must cover every query row
+    ws_bytes = lib.dax_attn_workspace_bytes(1, 2, 300, 300, _lib.DAX_ATTN_QK_BF16_PV_BF16)
+    rc = lib.dax_attn_forward_scatter(table(4096, 8192), 2, 100, _lib.DAX_BF16, 2, 300, 300, 128, 256, 0, 300,
+                                      _lib.DAX_ATTN_QK_BF16_PV_BF16, ctypes.c_void_p(1 << 20), ws_bytes, None)
+    assert rc == _lib.DAX_ERR_INVALID and b"destinations" in lib.dax_last_error()
+    assert lib.dax_peer_copy(None, one, 16, None) == _lib.DAX_ERR_INVALID
+    assert lib.dax_peer_copy(one, one, 0, None) == _lib.DAX_OK
