@@ -700,7 +700,7 @@ def main():
     # the factor an ncu capture of a 40-head, 16,384-token launch measured for this mode (K/V re-reads by the other
     # query tiles hit L2; traffic grows in proportion to rows x heads)
     q_b, kv_b = {"sage": (384.0, 256.0), "int8_bf16": (384.0, 384.0), "bf16": (512.0, 512.0)}[mode]
-    ncu_factor = {"sage": 0.936}.get(mode)
+    ncu_factor = {"sage": 0.936, "bf16": 0.975}.get(mode)
     traffic = (sum(ncu_factor * m[0] * m[1] * (q_b * m[2] + kv_b * m[3]) for m in metas) / calls) if calls and ncu_factor else None
     src = {"sage": "2 x", "bf16": "1 x", "int8_bf16": "4/3 x"}[mode]
     roofline = {"bound": "tensor", "kernel": f"attn_fwd_kernel<{mode}>", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
