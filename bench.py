@@ -260,6 +260,9 @@ def attention_kernel_ms(ops, heads: int, S: int, dev, repeats: int = 5):
     out = torch.empty((1, S, heads, HEAD_DIM), dtype=torch.bfloat16, device=dev).transpose(1, 2)
     res = {}
     for mode in MODES:
+        if mode == "bf16":  # reads Q, K, V in place: one kernel, nothing to prepare
+            res[mode] = {"forward_ms": time_events(lambda: ops.attention_direct(q, k, v, out), repeats, 2), "prepare_ms": 0.0}
+            continue
         prep = time_events(lambda: ops.attn_prepare(q, k, v, mode), 3, 1)
         plan = ops.attn_prepare(q, k, v, mode)
         fwd = time_events(lambda: ops.attn_forward(plan, out), repeats, 2)

@@ -37,6 +37,9 @@ SIGNATURES = {
     "dax_rmsnorm_rope_pack_scatter": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int,
                                               c_void_p, c_float, c_void_p, c_void_p, c_int64, POINTER(c_void_p), c_int64,
                                               c_int64, c_int64, c_void_p]),
+    "dax_attn_forward_direct": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, I64x3, I64x3,
+                                        I64x3, c_float, c_void_p, I64x3, POINTER(c_void_p), c_int64, c_int64, c_int64, c_int64,
+                                        c_int64, c_int64, c_void_p]),
     "dax_attn_forward_scatter": (c_int, [POINTER(c_void_p), c_int64, c_int64, c_int, c_int64, c_int64, c_int64, c_int64,
                                          c_int64, c_int64, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
     "dax_layernorm_modulate_quant": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p,

@@ -145,6 +145,18 @@ class DAXWanAttnProcessor2_0:
             self._xchg = shared_exchange()
         return self._xchg
 
+    def _direct(self) -> bool:
+        """The 16-bit mode reads Q, K, V in place (one kernel, no prepare step); the INT8-score modes prepare first."""
+        return ops.ATTN_MODES[self.attention_mode] == ops.ATTN_MODES["bf16"]
+
+    def _attend(self, q, k, v, out, **ranges) -> None:
+        """Attention of ``[1, h, S, 128]`` views into ``out`` (optionally for query ranges only)."""
+        if self._direct():
+            ops.attention_direct(q, k, v, out, sm_scale=1.0 / math.sqrt(HEAD_DIM), **ranges)
+        else:
+            plan = ops.attn_prepare(q, k, v, self.attention_mode, 1.0 / math.sqrt(HEAD_DIM))
+            ops.attn_forward(plan, out, **ranges)
+
     @staticmethod
     def _project(lin: nn.Module, x_rows: torch.Tensor, q_pair, *, out: torch.Tensor, ldo: int, col_group: int,
                  group_stride: int, row_sumsq: Optional[torch.Tensor], resid: Optional[torch.Tensor] = None,
@@ -277,14 +289,22 @@ class DAXWanAttnProcessor2_0:
         def bhsd(t):
             return t.view(1, S, h, HEAD_DIM).transpose(1, 2)
 
-        plan = ops.attn_prepare(bhsd(recv[0]), bhsd(recv[1]), bhsd(recv[2]), self.attention_mode,
-                                1.0 / math.sqrt(HEAD_DIM))
         attn_out = _BUFFERS.get("attn_out", (S, hd), dt, dev)
+        if self._direct():
+            def attend(**ranges):
+                ops.attention_direct(bhsd(recv[0]), bhsd(recv[1]), bhsd(recv[2]), bhsd(attn_out),
+                                     sm_scale=1.0 / math.sqrt(HEAD_DIM), **ranges)
+        else:
+            plan = ops.attn_prepare(bhsd(recv[0]), bhsd(recv[1]), bhsd(recv[2]), self.attention_mode,
+                                    1.0 / math.sqrt(HEAD_DIM))
+
+            def attend(**ranges):
+                ops.attn_forward(plan, bhsd(attn_out), **ranges)
         o_lin = attn.to_out[0]
         out = torch.empty((s, D), dtype=dt, device=dev)
 
         if P == 1:
-            ops.attn_forward(plan, bhsd(attn_out))
+            attend()
             pair = self._quantize_for((o_lin,), attn_out)[0]
             self._project(o_lin, attn_out, pair, out=out, ldo=D, col_group=D, group_stride=0, row_sumsq=None,
                           resid=resid, gate=gate)
@@ -315,7 +335,7 @@ class DAXWanAttnProcessor2_0:
             mine, sends = None, []
             for g in range(len(gb) - 1):
                 g0, g1 = gb[g], gb[g + 1]
-                ops.attn_forward(plan, bhsd(attn_out), q_begin=g0 * s, q_end=g1 * s)
+                attend(q_begin=g0 * s, q_end=g1 * s)
                 work = xchg.heads_to_tokens_group(attn_out, o_recv, s, range(g0, g1), async_op=True)
                 if g0 <= rank < g1:
                     mine = work
@@ -331,7 +351,7 @@ class DAXWanAttnProcessor2_0:
             b0, b1 = mb[i], mb[i + 1]
             if b1 == b0:
                 continue
-            ops.attn_forward(plan, bhsd(attn_out), q_begin=b0, q_end=b1, n_ranges=P, range_stride=s)
+            attend(q_begin=b0, q_end=b1, n_ranges=P, range_stride=s)
             o_recv = _BUFFERS.get(f"o_recv{i}", (P, b1 - b0, hd), dt, dev)
             work = xchg.heads_to_tokens(attn_out, o_recv, s, b0, b1, async_op=overlap)
             pending.append((work, o_recv, b0, b1))
@@ -397,18 +417,25 @@ class DAXWanAttnProcessor2_0:
         def bhsd(t):
             return t.view(1, S, h, HEAD_DIM).transpose(1, 2)
 
-        # K and V have landed everywhere well before the last Q rows have: their statistics and operand passes run
-        # under the tail of the Q transfer
-        main.wait_event(kv_sent)
-        peers.barrier(0)  # every rank's K and V rows are in my buffers
-        args = (bhsd(recv[0]), bhsd(recv[1]), bhsd(recv[2]), self.attention_mode, 1.0 / math.sqrt(HEAD_DIM))
-        ops.attn_prepare(*args, parts="kv")
-        main.wait_stream(side)
-        peers.barrier(2)  # ... and every rank's Q rows
-        plan = ops.attn_prepare(*args, parts="q")
         # query row q belongs to rank q // s: its result goes to slab `rank` of that rank's o_recv
         o_dests = [o_ptrs[d] + (rank * s * hd) * esz for d in range(P)]
-        ops.attn_forward_scatter(plan, o_dests, rows_per_dest=s, head_stride=HEAD_DIM, token_stride=hd)
+        if self._direct():
+            # the 16-bit kernel reads Q, K, V where they landed: nothing to prepare
+            main.wait_stream(side)
+            peers.barrier(0)  # every rank's Q, K and V rows are in my buffers
+            ops.attention_direct(bhsd(recv[0]), bhsd(recv[1]), bhsd(recv[2]), sm_scale=1.0 / math.sqrt(HEAD_DIM),
+                                 dest_ptrs=o_dests, rows_per_dest=s, head_stride=HEAD_DIM, token_stride=hd)
+        else:
+            # K and V have landed everywhere well before the last Q rows have: their statistics and operand passes run
+            # under the tail of the Q transfer
+            main.wait_event(kv_sent)
+            peers.barrier(0)  # every rank's K and V rows are in my buffers
+            args = (bhsd(recv[0]), bhsd(recv[1]), bhsd(recv[2]), self.attention_mode, 1.0 / math.sqrt(HEAD_DIM))
+            ops.attn_prepare(*args, parts="kv")
+            main.wait_stream(side)
+            peers.barrier(2)  # ... and every rank's Q rows
+            plan = ops.attn_prepare(*args, parts="q")
+            ops.attn_forward_scatter(plan, o_dests, rows_per_dest=s, head_stride=HEAD_DIM, token_stride=hd)
         peers.barrier(1)  # every rank's attention rows for my tokens have landed
         out = torch.empty((s, D), dtype=dt, device=dev)
         self._o_project(attn.to_out[0], (_Done(), o_recv, 0, s), out, P, hd, D, resid, gate)
@@ -466,8 +493,7 @@ class DAXWanAttnProcessor2_0:
             return t.view(1, n, H, HEAD_DIM).transpose(1, 2)
 
         o = _BUFFERS.get("xo", (s, D), dt, dev)
-        plan = ops.attn_prepare(bhsd(q, s), bhsd(k, Sk), bhsd(v, Sk), self.attention_mode, 1.0 / math.sqrt(HEAD_DIM))
-        ops.attn_forward(plan, bhsd(o, s))
+        self._attend(bhsd(q, s), bhsd(k, Sk), bhsd(v, Sk), bhsd(o, s))
         o_lin = attn.to_out[0]
         out = torch.empty((s, D), dtype=dt, device=dev)
         pair = self._quantize_for((o_lin,), o)[0]

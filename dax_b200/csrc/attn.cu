@@ -579,6 +579,8 @@ int attn_forward_entry(void* o, int dtype, int64_t B, int64_t heads, int64_t Sq,
   p.out_bf16 = dtype == DAX_BF16;
   p.dest = dest;
   p.rows_per_dest = static_cast<int>(rows_per_dest > 0 ? rows_per_dest : 1);
+  p.direct_cmul = 0.f;
+  p.in_fmt = 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (mode == DAX_ATTN_QK_I8_PV_F8) return launch_fwd<DAX_ATTN_QK_I8_PV_F8>(ws, p, B * heads, st);
   if (mode == DAX_ATTN_QK_I8_PV_BF16) return launch_fwd<DAX_ATTN_QK_I8_PV_BF16>(ws, p, B * heads, st);
@@ -607,4 +609,62 @@ extern "C" int dax_attn_forward_scatter(void* const* o_dest, int64_t n_dest, int
   int64_t strides[3] = {0, head_stride, token_stride};
   return dax::attn_forward_entry(base, dtype, 1, heads, Sq, Sk, strides, q_begin, q_end, 1, 0, tab, rows_per_dest, mode,
                                  workspace, workspace_bytes, stream);
+}
+
+extern "C" int dax_attn_forward_direct(const void* q, const void* k, const void* v, int dtype, int64_t B, int64_t heads,
+                                       int64_t Sq, int64_t Sk, int64_t q_strides[3], int64_t k_strides[3],
+                                       int64_t v_strides[3], float sm_scale, void* o, int64_t o_strides[3],
+                                       void* const* o_dest, int64_t n_dest, int64_t rows_per_dest, int64_t q_begin,
+                                       int64_t q_end, int64_t n_ranges, int64_t range_stride, void* stream) {
+  using namespace dax;
+  DAX_REQUIRE(q && k && v && q_strides && k_strides && v_strides && o_strides, DAX_ERR_INVALID, "attn_forward_direct: null pointer");
+  DAX_REQUIRE(dtype == DAX_BF16 || dtype == DAX_F16, DAX_ERR_UNSUPPORTED, "attn_forward_direct: dtype %d is not BF16/F16", dtype);
+  DAX_REQUIRE(B > 0 && heads > 0 && Sq > 0 && Sk > 0 && B * heads <= 65535 && Sq < (1ll << 31) - 256 && Sk < (1ll << 31) - 128,
+              DAX_ERR_INVALID, "attn_forward_direct: bad shape B=%lld heads=%lld Sq=%lld Sk=%lld", (long long)B,
+              (long long)heads, (long long)Sq, (long long)Sk);
+  DAX_REQUIRE(sm_scale > 0.f, DAX_ERR_INVALID, "attn_forward_direct: sm_scale must be positive");
+  const int64_t* ss[3] = {q_strides, k_strides, v_strides};
+  const void* ptrs[3] = {q, k, v};
+  for (int i = 0; i < 3; ++i) {
+    DAX_REQUIRE(aligned16(ptrs[i]) && ss[i][1] % 8 == 0 && ss[i][2] % 8 == 0 && ss[i][2] >= 128 && ss[i][1] > 0, DAX_ERR_ALIGN,
+                "attn_forward_direct: q, k, v must be 16-byte aligned with head / token strides that are multiples of 8 elements");
+    // the 3-D tensor map flattens (batch, head) into one dimension of stride = head stride
+    DAX_REQUIRE(B == 1 || ss[i][0] == heads * ss[i][1], DAX_ERR_UNSUPPORTED,
+                "attn_forward_direct: batch stride must equal heads x head stride (or batch 1)");
+  }
+  DAX_REQUIRE(q_begin >= 0 && q_begin <= q_end && q_end <= Sq, DAX_ERR_INVALID,
+              "attn_forward_direct: bad query range [%lld, %lld) for Sq=%lld", (long long)q_begin, (long long)q_end, (long long)Sq);
+  DAX_REQUIRE(n_ranges >= 1 && (n_ranges == 1 || range_stride >= q_end - q_begin) && q_end + (n_ranges - 1) * range_stride <= Sq,
+              DAX_ERR_INVALID, "attn_forward_direct: %lld ranges of stride %lld do not fit Sq=%lld", (long long)n_ranges,
+              (long long)range_stride, (long long)Sq);
+  GroupTable dest{};
+  void* base = o;
+  if (n_dest > 0) {
+    int rc = make_group_table(o_dest, n_dest, 2, &dest, &base);
+    if (rc != DAX_OK) return rc;
+    DAX_REQUIRE(B == 1 && rows_per_dest > 0 && n_dest * rows_per_dest >= Sq && n_ranges == 1, DAX_ERR_INVALID,
+                "attn_forward_direct: %lld destinations of %lld rows do not cover Sq=%lld (batch 1, one range)", (long long)n_dest,
+                (long long)rows_per_dest, (long long)Sq);
+  }
+  DAX_REQUIRE(base != nullptr && aligned16(base) && o_strides[0] % 8 == 0 && o_strides[1] % 8 == 0 && o_strides[2] % 8 == 0,
+              DAX_ERR_ALIGN, "attn_forward_direct: o must be 16-byte aligned with strides that are multiples of 8 elements");
+  if (q_begin == q_end) return DAX_OK;
+  AttnParams p{};
+  p.o = base;
+  p.status = device_status_ptr();
+  DAX_REQUIRE(p.status != nullptr, DAX_ERR_CUDA, "attn_forward_direct: cannot resolve the device status word");
+  p.o_sb = o_strides[0]; p.o_sh = o_strides[1]; p.o_st = o_strides[2];
+  p.heads = static_cast<int>(heads);
+  p.Sq = static_cast<int>(Sq); p.Sk = static_cast<int>(Sk);
+  p.Sq_pad = static_cast<int>(round_up(Sq, 256)); p.Sk_pad = static_cast<int>(round_up(Sk, 128));
+  p.q_begin = static_cast<int>(q_begin); p.q_end = static_cast<int>(q_end);
+  p.n_ranges = static_cast<int>(n_ranges); p.range_stride = static_cast<int>(range_stride);
+  p.tiles_per_range = static_cast<int>((q_end - q_begin + 255) / 256);
+  p.out_bf16 = dtype == DAX_BF16;
+  p.dest = dest;
+  p.rows_per_dest = static_cast<int>(rows_per_dest > 0 ? rows_per_dest : 1);
+  p.direct_cmul = sm_scale * 1.4426950408889634f;
+  p.in_fmt = dtype == DAX_BF16 ? 1 : 0;
+  return launch_attn_fwd_tmem_p_direct(q, k, v, q_strides[1], q_strides[2], k_strides[1], k_strides[2], v_strides[1],
+                                       v_strides[2], p, B * heads, static_cast<cudaStream_t>(stream));
 }

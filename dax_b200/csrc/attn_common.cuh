@@ -47,6 +47,10 @@ struct AttnParams {
   // sequence-parallel attention written by the kernel itself, each destination being another GPU's buffer)
   GroupTable dest;
   int rows_per_dest;
+  // direct mode of the bf16 kernel (operands read in place, no prepare step): score multiplier
+  // softmax_scale * log2(e), and the 16-bit format of Q / K / V (1 = bf16, 0 = f16)
+  float direct_cmul;
+  int in_fmt;
 };
 
 // Address of output row q_row of (batch b, head h), element units.
@@ -110,5 +114,8 @@ inline int attn_workspace_layout(int64_t B, int64_t heads, int64_t Sq, int64_t S
 
 // bf16 Q.K^T + bf16 P.V with the probabilities kept in tensor memory (attn_tmem.cu)
 int launch_attn_fwd_tmem_p(const AttnWorkspace& ws, const AttnParams& p, int64_t BH, cudaStream_t st);
+// the same kernel reading Q, K, V in place: [BH, S, 128] with element strides (head, token), channels contiguous
+int launch_attn_fwd_tmem_p_direct(const void* q, const void* k, const void* v, int64_t q_sh, int64_t q_st, int64_t k_sh,
+                                  int64_t k_st, int64_t v_sh, int64_t v_st, const AttnParams& p, int64_t BH, cudaStream_t st);
 
 }  // namespace dax

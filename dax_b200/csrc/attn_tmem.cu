@@ -76,6 +76,9 @@ __device__ __forceinline__ uint32_t pack_bf16x2_trunc(float a, float b) {
   return r;
 }
 
+// DIRECT: Q, K and V are read in place from [BH, S, 128] tensors (3-D TMA maps, rows past the end read as zero);
+// V is then a [keys x channels] tile, i.e. the B operand of P.V with N (channels) contiguous: MN-major descriptor.
+template <bool DIRECT>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_fwd_tmem_p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
@@ -135,15 +138,21 @@ attn_fwd_tmem_p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         mbar_arrive_expect_tx(q_full, 2 * TILE_BYTES);
         const int q_row = bh * p.Sq_pad + q0;
         for (int x = 0; x < 2; ++x)
-          for (int sub = 0; sub < 2; ++sub)
-            tma_load_2d(smem + OFF_Q + x * TILE_BYTES + sub * BOX_BYTES, &map_q, q_full, sub * 64, q_row + x * 128);
+          for (int sub = 0; sub < 2; ++sub) {
+            uint8_t* dst = smem + OFF_Q + x * TILE_BYTES + sub * BOX_BYTES;
+            if constexpr (DIRECT) tma_load_3d(dst, &map_q, q_full, sub * 64, q0 + x * 128, bh);
+            else tma_load_2d(dst, &map_q, q_full, sub * 64, q_row + x * 128);
+          }
         for (int seq = 0; seq < 2 * n_kv; ++seq) {
           const int j = seq >> 1;
           const uint32_t s = seq % NSLOT, ph = (seq / NSLOT) & 1u;
           if (!mbar_wait(&kv_empty[s], ph ^ 1u, abort_flag)) break;
           mbar_arrive_expect_tx(&kv_full[s], TILE_BYTES);
           uint8_t* dst = smem + OFF_RING + s * TILE_BYTES;
-          if ((seq & 1) == 0) {  // K_j : [128 tokens x 128 channels]
+          if constexpr (DIRECT) {  // K_j, V_j : [128 tokens x 128 channels], two boxes of 64 channels
+            for (int sub = 0; sub < 2; ++sub)
+              tma_load_3d(dst + sub * BOX_BYTES, (seq & 1) == 0 ? &map_k : &map_v, &kv_full[s], sub * 64, j * 128, bh);
+          } else if ((seq & 1) == 0) {  // K_j : [128 tokens x 128 channels]
             for (int sub = 0; sub < 2; ++sub)
               tma_load_2d(dst + sub * BOX_BYTES, &map_k, &kv_full[s], sub * 64, bh * p.Sk_pad + j * 128);
           } else {               // V_j^T : [128 channels x 128 tokens]
@@ -158,7 +167,11 @@ attn_fwd_tmem_p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // issues the tensor-core instructions and the commits.
       {
         const bool leader = elect_one();
-        constexpr uint32_t idesc = make_idesc(1, 1, 1, 128, 128);  // bf16 x bf16 -> f32, M = N = 128
+        // f32 accumulators, M = N = 128.  Q.K^T multiplies the input format by itself; P is always bf16; in direct mode
+        // the B operand of P.V (V as stored: channels contiguous) is MN-major (bit 16)
+        const uint32_t fmt = DIRECT ? static_cast<uint32_t>(p.in_fmt) : 1u;
+        const uint32_t idesc_qk = make_idesc(1, fmt, fmt, 128, 128);
+        const uint32_t idesc_pv = make_idesc(1, 1, fmt, 128, 128) | (DIRECT ? (1u << 16) : 0u);
         const uint32_t q_base = smem_u32(smem + OFF_Q);
         const uint32_t ring = smem_u32(smem + OFF_RING);
         const uint32_t s_tm = tmem_base;
@@ -176,7 +189,7 @@ attn_fwd_tmem_p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const uint64_t adv = static_cast<uint64_t>((i >> 2) * (BOX_BYTES >> 4) + 2 * (i & 3));
-              umma_ss<KIND_F16>(s_tm, q_desc + adv, k_desc + adv, idesc, i != 0 ? 1u : 0u);
+              umma_ss<KIND_F16>(s_tm, q_desc + adv, k_desc + adv, idesc_qk, i != 0 ? 1u : 0u);
             }
             umma_commit(&s_full[x]);
             umma_commit(&kv_empty[slot]);
@@ -191,14 +204,17 @@ attn_fwd_tmem_p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           if (!mbar_wait(&kv_full[slot], ph, abort_flag)) return false;
           if (!mbar_wait(&p_full[x], j & 1u, abort_flag)) return false;
           tc_fence_after_sync();
-          const uint64_t v_desc = make_desc_k_sw128(ring + slot * TILE_BYTES);
+          const uint64_t v_desc = DIRECT ? make_desc_mn_sw128(ring + slot * TILE_BYTES, BOX_BYTES)
+                                         : make_desc_k_sw128(ring + slot * TILE_BYTES);
           const uint32_t p_tm = tmem_base + 128 + x * 64;
           const uint32_t o_tm = tmem_base + 256 + x * 128;
           if (leader) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              const uint64_t adv = static_cast<uint64_t>((i >> 2) * (BOX_BYTES >> 4) + 2 * (i & 3));
-              umma_ts_f16(o_tm, p_tm + 8 * i, v_desc + adv, idesc, (j > 0 || i != 0) ? 1u : 0u);
+              // 16 keys further: K-major V^T = 32 bytes along the row (second box after 64 keys); MN-major V = 16 rows
+              const uint64_t adv = DIRECT ? static_cast<uint64_t>(i * ((16 * 128) >> 4))
+                                          : static_cast<uint64_t>((i >> 2) * (BOX_BYTES >> 4) + 2 * (i & 3));
+              umma_ts_f16(o_tm, p_tm + 8 * i, v_desc + adv, idesc_pv, (j > 0 || i != 0) ? 1u : 0u);
             }
             umma_commit(&pv_done[x]);
             umma_commit(&kv_empty[slot]);
@@ -228,7 +244,8 @@ attn_fwd_tmem_p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t o_tmem = tmem_base + lane_base + 256 + x * 128;
     const int q_row = q0 + x * 128 + r;
     // 16-bit scores are unscaled: the per-row factor (softmax scale * log2 e) multiplies them here
-    const float cmul = q_row < p.Sq ? p.q_scale[static_cast<int64_t>(bh) * p.Sq_pad + q_row] : 1.f;
+    const float cmul = DIRECT ? p.direct_cmul
+                              : (q_row < p.Sq ? p.q_scale[static_cast<int64_t>(bh) * p.Sq_pad + q_row] : 1.f);
     float m = -INFINITY, l = 0.f;
     bool ok = true;
 
@@ -367,8 +384,28 @@ int launch_attn_fwd_tmem_p(const AttnWorkspace& ws, const AttnParams& p, int64_t
     if (rc != DAX_OK) return rc;
   }
   dim3 grid(static_cast<unsigned>(p.n_ranges * p.tiles_per_range), static_cast<unsigned>(BH));
-  DAX_CUDA(cudaFuncSetAttribute(attn_fwd_tmem_p_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
-  attn_fwd_tmem_p_kernel<<<grid, THREADS, SMEM_TOTAL, st>>>(map_q, map_k, map_v, p);
+  DAX_CUDA(cudaFuncSetAttribute(attn_fwd_tmem_p_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
+  attn_fwd_tmem_p_kernel<false><<<grid, THREADS, SMEM_TOTAL, st>>>(map_q, map_k, map_v, p);
+  DAX_CUDA(cudaGetLastError());
+  return DAX_OK;
+}
+
+int launch_attn_fwd_tmem_p_direct(const void* q, const void* k, const void* v, int64_t q_sh, int64_t q_st, int64_t k_sh,
+                                  int64_t k_st, int64_t v_sh, int64_t v_st, const AttnParams& p, int64_t BH, cudaStream_t st) {
+  CUtensorMap maps[3];
+  const void* base[3] = {q, k, v};
+  const int64_t sh[3] = {q_sh, k_sh, v_sh}, stt[3] = {q_st, k_st, v_st};
+  const int64_t rows[3] = {p.Sq, p.Sk, p.Sk};
+  for (int i = 0; i < 3; ++i) {
+    uint64_t dims[3] = {128, static_cast<uint64_t>(rows[i]), static_cast<uint64_t>(BH)};
+    uint64_t strides[3] = {2, static_cast<uint64_t>(stt[i]) * 2, static_cast<uint64_t>(sh[i]) * 2};
+    uint32_t box[3] = {64, 128, 1};
+    int rc = make_tma_map(&maps[i], base[i], 2, 3, dims, strides, box);
+    if (rc != DAX_OK) return rc;
+  }
+  dim3 grid(static_cast<unsigned>(p.n_ranges * p.tiles_per_range), static_cast<unsigned>(BH));
+  DAX_CUDA(cudaFuncSetAttribute(attn_fwd_tmem_p_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
+  attn_fwd_tmem_p_kernel<true><<<grid, THREADS, SMEM_TOTAL, st>>>(maps[0], maps[1], maps[2], p);
   DAX_CUDA(cudaGetLastError());
   return DAX_OK;
 }

@@ -191,6 +191,20 @@ __device__ __forceinline__ uint64_t make_desc_k_sw128(uint32_t smem_addr) {
   return d;
 }
 
+// The same for an MN-major operand (the non-contracted dimension contiguous): rows of 128 bytes = 64 16-bit elements
+// along MN, one row per K index, 128-byte swizzle over groups of 8 rows (again what a TMA box with inner extent 128 B
+// writes).  Stride byte offset = the next 8 K-rows (1024 B); leading byte offset = the next 64 MN-elements, i.e. the
+// next box, `mn_block_bytes` further.  A K step of 16 = 16 rows = 2048 B on the start address.
+__device__ __forceinline__ uint64_t make_desc_mn_sw128(uint32_t smem_addr, uint32_t mn_block_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((mn_block_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
 // Instruction descriptor (upper 32 bits of the "idesc" operand).
 //   [4,6) accumulator format: 1 = f32, 2 = s32     [7,10) A format   [10,13) B format
 //   [15] A major (0 = K)   [16] B major (0 = K)     [17,23) N >> 3    [24,29) M >> 4

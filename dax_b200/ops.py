@@ -353,13 +353,45 @@ def attn_forward_scatter(plan: AttentionPlan, dest_ptrs, rows_per_dest: int, hea
     TRACE.end(tok, (plan.B, plan.heads, q_end - q_begin, plan.Sk))
 
 
+def attention_direct(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[torch.Tensor] = None, *,
+                     sm_scale: Optional[float] = None, dest_ptrs=None, rows_per_dest: int = 0, head_stride: int = 0,
+                     token_stride: int = 0, q_begin: int = 0, q_end: Optional[int] = None, n_ranges: int = 1,
+                     range_stride: int = 0) -> Optional[torch.Tensor]:
+    """The 16-bit attention reading ``q, k, v`` (``[B, heads, S, 128]`` views, bf16 or fp16) in place: one kernel, no
+    prepare step, no workspace.  Result into ``out`` (a ``[B, heads, Sq, 128]`` view; allocated token-major when
+    omitted) or, with ``dest_ptrs``, scattered by destination like ``attn_forward_scatter``."""
+    _need_cuda(q, k, v, out)
+    B, heads, Sq, d = q.shape
+    Sk = k.shape[2]
+    assert d == 128 and k.shape == v.shape and k.shape[:2] == q.shape[:2] and q.dtype == k.dtype == v.dtype
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(d)
+    if q_end is None:
+        q_end = Sq
+    if dest_ptrs is not None:
+        o_ptr, o_str, table, n = None, I64x3(0, head_stride, token_stride), _ptr_array(dest_ptrs), len(dest_ptrs)
+    else:
+        if out is None:
+            out = torch.empty((B, Sq, heads, d), dtype=q.dtype, device=q.device).transpose(1, 2)
+        assert out.shape == (B, heads, Sq, 128) and out.dtype == q.dtype
+        o_ptr, o_str, table, n = out.data_ptr(), _bhsd_strides(out), None, 0
+    tok = TRACE.begin("attn_forward")
+    check(load().dax_attn_forward_direct(q.data_ptr(), k.data_ptr(), v.data_ptr(), _dt(q.dtype), B, heads, Sq, Sk,
+                                         _bhsd_strides(q), _bhsd_strides(k), _bhsd_strides(v), float(sm_scale), o_ptr, o_str,
+                                         table, n, rows_per_dest, q_begin, q_end, n_ranges, range_stride, _stream()))
+    TRACE.end(tok, (B, heads, (q_end - q_begin) * n_ranges, Sk))
+    return out
+
+
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mode: str = "bf16",
               sm_scale: Optional[float] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Non-causal attention over ``[B, heads, S, 128]``; the result has the memory layout
     ``[B, S, heads, 128]`` (token-major, as the head->sequence exchange wants it) viewed as
     ``[B, heads, S, 128]``."""
+    B, heads, Sq, d = q.shape
+    if ATTN_MODES[mode] == _lib.DAX_ATTN_QK_BF16_PV_BF16 and (B == 1 or all(t.stride(0) == heads * t.stride(1) for t in (q, k, v))):
+        return attention_direct(q, k, v, out, sm_scale=sm_scale)  # the 16-bit mode reads its operands in place
     plan = attn_prepare(q, k, v, mode, sm_scale)
     if out is None:
-        B, heads, Sq, d = q.shape
         out = torch.empty((B, Sq, heads, d), dtype=q.dtype, device=q.device).transpose(1, 2)
     return attn_forward(plan, out)

@@ -258,6 +258,19 @@ int dax_attn_forward_scatter(void* const* o_dest, int64_t n_dest, int64_t rows_p
                              int64_t Sq, int64_t Sk, int64_t head_stride, int64_t token_stride, int64_t q_begin,
                              int64_t q_end, int mode, void* workspace, size_t workspace_bytes, void* stream);
 
+/* The 16-bit attention (bf16 / f16 Q.K^T and P.V, the mode that stays within rel-L2 1e-2 of fp32 SDPA) in ONE call,
+ * reading q, k, v in place: no prepare step, no workspace.  The kernel's TMA maps address the [B, heads, S, 128] views
+ * directly (batch stride = heads x head stride, or B = 1), V is consumed as stored (its tile is the MN-major operand of
+ * P.V), K is not mean-smoothed (smoothing serves the INT8 range; softmax is invariant to it).  Replaces the dispatch at
+ * dax/adapters/wan/attn_adapter.py:198-229 like dax_attn_forward.  Output either to o (strides as in dax_attn_forward,
+ * with query ranges) or, with n_dest > 0, scattered by destination as in dax_attn_forward_scatter (o_strides[1] /
+ * o_strides[2] = head / token stride inside a destination; o may be NULL). */
+int dax_attn_forward_direct(const void* q, const void* k, const void* v, int dtype, int64_t B, int64_t heads,
+                            int64_t Sq, int64_t Sk, int64_t q_strides[3], int64_t k_strides[3], int64_t v_strides[3],
+                            float sm_scale, void* o, int64_t o_strides[3], void* const* o_dest, int64_t n_dest,
+                            int64_t rows_per_dest, int64_t q_begin, int64_t q_end, int64_t n_ranges,
+                            int64_t range_stride, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -434,3 +434,40 @@ def test_scatter_entry_points_match_the_strided_ones(ops):
         assert O.rel_l2(got, ref) <= tol and all(bool((t[0] == 7.0).all()) for t in dests)
     with pytest.raises(ValueError):
         ops.rmsnorm_rope_pack(xx, norm_weight=None, do_norm=False, ldo=hd, col_group=hd, group_ptrs=[one.data_ptr()] * 3)
+
+
+@pytest.mark.parametrize("B,H,Sq,Sk,dtype", [(1, 3, 1, 1, torch.bfloat16), (1, 3, 128, 128, torch.bfloat16),
+                                             (1, 3, 1000, 1000, torch.bfloat16), (2, 2, 300, 77, torch.float16),
+                                             (1, 2, 2049, 2049, torch.bfloat16)])
+def test_attention_direct(ops, B, H, Sq, Sk, dtype):
+    """The 16-bit attention reading Q, K, V in place (3-D tensor maps over the strided views, V as the MN-major operand
+    of P.V, no K smoothing, no workspace): head-major and token-major memory, against fp32 SDPA at the stated
+    tolerance, and against the prepared-operand variant of the same kernel."""
+    q, k, v = qkv(B, H, Sq, Sk, dtype=dtype, seed=Sq + Sk)
+    ref = O.sdpa_fp32(q, k, v)
+    tm = lambda t: t.transpose(1, 2).contiguous().to(DEV).transpose(1, 2)
+    for qq, kk, vv in ((q.to(DEV), k.to(DEV), v.to(DEV)), (tm(q), tm(k), tm(v))):
+        o = ops.attention_direct(qq, kk, vv).float().cpu()
+        assert not torch.isnan(o).any()
+        assert O.rel_l2(o, ref) <= 1e-2 and O.cosine(o, ref) >= 0.999
+    plan = ops.attn_prepare(q.to(DEV), k.to(DEV), v.to(DEV), "bf16")
+    o2 = torch.empty((B, Sq, H, 128), dtype=dtype, device=DEV).transpose(1, 2)
+    ops.attn_forward(plan, o2)
+    assert O.rel_l2(o, o2.float().cpu()) <= 6e-3
+
+
+def test_attention_direct_ranges_and_destinations(ops):
+    q, k, v = qkv(1, 2, 600, 600, seed=9)
+    ref = O.sdpa_fp32(q, k, v)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    out = torch.full((1, 600, 2, 128), 7.0, dtype=torch.bfloat16, device=DEV).transpose(1, 2)
+    ops.attention_direct(qd, kd, vd, out, q_begin=75, q_end=150, n_ranges=4, range_stride=150)
+    got = out.float().cpu()
+    for r in range(4):
+        lo, hi = r * 150 + 75, r * 150 + 150
+        assert O.rel_l2(got[:, :, lo:hi], ref[:, :, lo:hi]) <= 1e-2 and bool((got[:, :, r * 150:lo] == 7.0).all())
+    dests = [torch.full((2, 200, 2 * 128), 7.0, dtype=torch.bfloat16, device=DEV) for _ in range(3)]
+    ops.attention_direct(qd, kd, vd, dest_ptrs=[t[1].data_ptr() for t in dests], rows_per_dest=200, head_stride=128,
+                         token_stride=256)
+    got = torch.cat([t[1].view(200, 2, 128) for t in dests], 0).permute(1, 0, 2).unsqueeze(0).float().cpu()
+    assert O.rel_l2(got, ref) <= 1e-2 and all(bool((t[0] == 7.0).all()) for t in dests)
