@@ -145,13 +145,15 @@ class DAXWanAttnProcessor2_0:
             self._xchg = shared_exchange()
         return self._xchg
 
-    def _direct(self) -> bool:
-        """The 16-bit mode reads Q, K, V in place (one kernel, no prepare step); the INT8-score modes prepare first."""
-        return ops.ATTN_MODES[self.attention_mode] == ops.ATTN_MODES["bf16"]
+    def _direct(self, dtype=torch.bfloat16, S: int = 128, Sk: int = 128) -> bool:
+        """The 16-bit mode reads bf16 Q, K, V in place (one kernel, no prepare step) when there is at least one tile of
+        queries and keys; the INT8-score modes, fp16 tensors and tiny sequences prepare first."""
+        return (ops.ATTN_MODES[self.attention_mode] == ops.ATTN_MODES["bf16"] and dtype == torch.bfloat16
+                and S >= 128 and Sk >= 128)
 
     def _attend(self, q, k, v, out, **ranges) -> None:
         """Attention of ``[1, h, S, 128]`` views into ``out`` (optionally for query ranges only)."""
-        if self._direct():
+        if self._direct(q.dtype, q.shape[2], k.shape[2]):
             ops.attention_direct(q, k, v, out, sm_scale=1.0 / math.sqrt(HEAD_DIM), **ranges)
         else:
             plan = ops.attn_prepare(q, k, v, self.attention_mode, 1.0 / math.sqrt(HEAD_DIM))
@@ -290,7 +292,7 @@ class DAXWanAttnProcessor2_0:
             return t.view(1, S, h, HEAD_DIM).transpose(1, 2)
 
         attn_out = _BUFFERS.get("attn_out", (S, hd), dt, dev)
-        if self._direct():
+        if self._direct(dt, S, S):
             def attend(**ranges):
                 ops.attention_direct(bhsd(recv[0]), bhsd(recv[1]), bhsd(recv[2]), bhsd(attn_out),
                                      sm_scale=1.0 / math.sqrt(HEAD_DIM), **ranges)
@@ -389,37 +391,44 @@ class DAXWanAttnProcessor2_0:
         main = torch.cuda.current_stream()
         side = _side_stream(dev)
         send = [_BUFFERS.get(f"send{i}", (P, s, hd), dt, dev) for i in range(3)]
+        kv_sent = None
         for i in (2, 1, 0):
             lin, norm = lins[i], norms[i]
-            own = recv[i, rank * s:(rank + 1) * s]
-            groups = [own.data_ptr() if p == rank else send[i][p].data_ptr() for p in range(P)]
             plain = norm is None and (i == 2 or cos is None)
-            if plain and isinstance(lin, QLinear):
-                self._project(lin, x, pairs[i], out=None, ldo=hd, col_group=hd, group_stride=0, row_sumsq=None,
-                              group_ptrs=groups)
-            else:
-                tmp = _BUFFERS.get("proj_tmp", (s, D), dt, dev)
-                fused = isinstance(lin, QLinear) and norm is not None
-                ss = _BUFFERS.get("row_sumsq", (s, n_tiles), torch.float32, dev) if fused else None
-                self._project(lin, x, pairs[i], out=tmp, ldo=D, col_group=D, group_stride=0, row_sumsq=ss)
-                rope = i != 2 and cos is not None
-                ops.rmsnorm_rope_pack(tmp, norm_weight=getattr(norm, "weight", None) if norm is not None else None,
-                                      do_norm=norm is not None, eps=getattr(norm, "eps", 1e-6) if norm is not None else 1e-6,
-                                      rope_cos=cos if rope else None, rope_sin=sin if rope else None, token_offset=rank * s,
-                                      row_sumsq=ss, ldo=hd, col_group=hd, group_ptrs=groups)
-            side.wait_stream(main)
-            for dp in range(1, P):
-                p = (rank + dp) % P  # every rank starts with a different destination
-                # rank p owns head group p: my rows of tensor i land at rows [rank * s, (rank + 1) * s) of ITS buffer
-                ops.peer_copy(recv_ptrs[p] + ((i * S + rank * s) * hd) * esz, send[i][p], stream=side)
+            # the last tensor (Q) is projected in two row halves, so that only the second half's transfer (a sixth of
+            # the layer's Q/K/V bytes) is still in flight when the attention could start
+            bounds = chunk_bounds(s, 2) if (i == 0 and self._direct(dt, S, S)) else [0, s]
+            for c0, c1 in zip(bounds[:-1], bounds[1:]):
+                own = recv[i, rank * s + c0:rank * s + c1]
+                groups = [own.data_ptr() if p == rank else send[i][p, c0:c1].data_ptr() for p in range(P)]
+                pair = None if pairs[i] is None else (pairs[i][0][c0:c1], pairs[i][1][c0:c1])
+                if plain and isinstance(lin, QLinear):
+                    self._project(lin, x[c0:c1], pair, out=None, ldo=hd, col_group=hd, group_stride=0, row_sumsq=None,
+                                  group_ptrs=groups)
+                else:
+                    tmp = _BUFFERS.get("proj_tmp", (s, D), dt, dev)[c0:c1]
+                    fused = isinstance(lin, QLinear) and norm is not None
+                    ss = _BUFFERS.get("row_sumsq", (s, n_tiles), torch.float32, dev)[c0:c1] if fused else None
+                    self._project(lin, x[c0:c1], pair, out=tmp, ldo=D, col_group=D, group_stride=0, row_sumsq=ss)
+                    rope = i != 2 and cos is not None
+                    ops.rmsnorm_rope_pack(tmp, norm_weight=getattr(norm, "weight", None) if norm is not None else None,
+                                          do_norm=norm is not None, eps=getattr(norm, "eps", 1e-6) if norm is not None else 1e-6,
+                                          rope_cos=cos if rope else None, rope_sin=sin if rope else None,
+                                          token_offset=rank * s + c0, row_sumsq=ss, ldo=hd, col_group=hd, group_ptrs=groups)
+                side.wait_stream(main)
+                for dp in range(1, P):
+                    p = (rank + dp) % P  # every rank starts with a different destination
+                    # rank p owns head group p: my rows of tensor i land at rows [rank * s, (rank + 1) * s) of ITS buffer
+                    ops.peer_copy(recv_ptrs[p] + ((i * S + rank * s + c0) * hd) * esz, send[i][p, c0:c1], stream=side)
             if i == 1:
                 kv_sent = side.record_event()
+
         def bhsd(t):
             return t.view(1, S, h, HEAD_DIM).transpose(1, 2)
 
         # query row q belongs to rank q // s: its result goes to slab `rank` of that rank's o_recv
         o_dests = [o_ptrs[d] + (rank * s * hd) * esz for d in range(P)]
-        if self._direct():
+        if self._direct(dt, S, S):
             # the 16-bit kernel reads Q, K, V where they landed: nothing to prepare
             main.wait_stream(side)
             peers.barrier(0)  # every rank's Q, K and V rows are in my buffers

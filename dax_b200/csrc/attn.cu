@@ -618,7 +618,12 @@ extern "C" int dax_attn_forward_direct(const void* q, const void* k, const void*
                                        int64_t q_end, int64_t n_ranges, int64_t range_stride, void* stream) {
   using namespace dax;
   DAX_REQUIRE(q && k && v && q_strides && k_strides && v_strides && o_strides, DAX_ERR_INVALID, "attn_forward_direct: null pointer");
-  DAX_REQUIRE(dtype == DAX_BF16 || dtype == DAX_F16, DAX_ERR_UNSUPPORTED, "attn_forward_direct: dtype %d is not BF16/F16", dtype);
+  // bf16 only: P is produced as bf16 (truncation), and both operands of one kind::f16 product take the same format here;
+  // sequences of at least one tile, so that no tensor-map box is larger than the tensor it reads
+  DAX_REQUIRE(dtype == DAX_BF16, DAX_ERR_UNSUPPORTED, "attn_forward_direct: dtype %d is not BF16 (use dax_attn_prepare + dax_attn_forward)", dtype);
+  DAX_REQUIRE(Sq >= 128 && Sk >= 128, DAX_ERR_UNSUPPORTED,
+              "attn_forward_direct: Sq=%lld, Sk=%lld: sequences shorter than 128 go through dax_attn_prepare + dax_attn_forward",
+              (long long)Sq, (long long)Sk);
   DAX_REQUIRE(B > 0 && heads > 0 && Sq > 0 && Sk > 0 && B * heads <= 65535 && Sq < (1ll << 31) - 256 && Sk < (1ll << 31) - 128,
               DAX_ERR_INVALID, "attn_forward_direct: bad shape B=%lld heads=%lld Sq=%lld Sk=%lld", (long long)B,
               (long long)heads, (long long)Sq, (long long)Sk);
@@ -664,7 +669,7 @@ extern "C" int dax_attn_forward_direct(const void* q, const void* k, const void*
   p.dest = dest;
   p.rows_per_dest = static_cast<int>(rows_per_dest > 0 ? rows_per_dest : 1);
   p.direct_cmul = sm_scale * 1.4426950408889634f;
-  p.in_fmt = dtype == DAX_BF16 ? 1 : 0;
+  p.in_fmt = 1;
   return launch_attn_fwd_tmem_p_direct(q, k, v, q_strides[1], q_strides[2], k_strides[1], k_strides[2], v_strides[1],
                                        v_strides[2], p, B * heads, static_cast<cudaStream_t>(stream));
 }

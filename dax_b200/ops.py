@@ -353,6 +353,14 @@ def attn_forward_scatter(plan: AttentionPlan, dest_ptrs, rows_per_dest: int, hea
     TRACE.end(tok, (plan.B, plan.heads, q_end - q_begin, plan.Sk))
 
 
+def direct_attention_ok(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mode: str) -> bool:
+    """Whether the in-place 16-bit kernel serves this call: bf16 mode and tensors, at least one tile of queries and
+    keys, (batch, head) flattening to one stride."""
+    B, heads = q.shape[:2]
+    return (ATTN_MODES[mode] == _lib.DAX_ATTN_QK_BF16_PV_BF16 and q.dtype == torch.bfloat16 and q.shape[2] >= 128
+            and k.shape[2] >= 128 and (B == 1 or all(t.stride(0) == heads * t.stride(1) for t in (q, k, v))))
+
+
 def attention_direct(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[torch.Tensor] = None, *,
                      sm_scale: Optional[float] = None, dest_ptrs=None, rows_per_dest: int = 0, head_stride: int = 0,
                      token_stride: int = 0, q_begin: int = 0, q_end: Optional[int] = None, n_ranges: int = 1,
@@ -389,7 +397,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mode: str = "bf
     ``[B, S, heads, 128]`` (token-major, as the head->sequence exchange wants it) viewed as
     ``[B, heads, S, 128]``."""
     B, heads, Sq, d = q.shape
-    if ATTN_MODES[mode] == _lib.DAX_ATTN_QK_BF16_PV_BF16 and (B == 1 or all(t.stride(0) == heads * t.stride(1) for t in (q, k, v))):
+    if direct_attention_ok(q, k, v, mode):
         return attention_direct(q, k, v, out, sm_scale=sm_scale)  # the 16-bit mode reads its operands in place
     plan = attn_prepare(q, k, v, mode, sm_scale)
     if out is None:

@@ -258,8 +258,9 @@ int dax_attn_forward_scatter(void* const* o_dest, int64_t n_dest, int64_t rows_p
                              int64_t Sq, int64_t Sk, int64_t head_stride, int64_t token_stride, int64_t q_begin,
                              int64_t q_end, int mode, void* workspace, size_t workspace_bytes, void* stream);
 
-/* The 16-bit attention (bf16 / f16 Q.K^T and P.V, the mode that stays within rel-L2 1e-2 of fp32 SDPA) in ONE call,
- * reading q, k, v in place: no prepare step, no workspace.  The kernel's TMA maps address the [B, heads, S, 128] views
+/* The 16-bit attention (bf16 Q.K^T and P.V, the mode that stays within rel-L2 1e-2 of fp32 SDPA) in ONE call,
+ * reading q, k, v in place: no prepare step, no workspace.  dtype BF16 only, Sq and Sk at least 128 (anything else:
+ * DAX_ERR_UNSUPPORTED, use dax_attn_prepare + dax_attn_forward).  The kernel's TMA maps address the [B, heads, S, 128] views
  * directly (batch stride = heads x head stride, or B = 1), V is consumed as stored (its tile is the MN-major operand of
  * P.V), K is not mean-smoothed (smoothing serves the INT8 range; softmax is invariant to it).  Replaces the dispatch at
  * dax/adapters/wan/attn_adapter.py:198-229 like dax_attn_forward.  Output either to o (strides as in dax_attn_forward,
