@@ -22,6 +22,7 @@ per-head operation, so this equals the reference's rotation after the exchange
 from __future__ import annotations
 
 import math
+from types import SimpleNamespace
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -368,7 +369,14 @@ class DAXWanAttnProcessor2_0:
         by copy engine while the next projection runs, the attention kernel stores every result row straight into the
         buffer of the rank that owns the token (free inside a compute-bound kernel), two device-side barriers order
         the ranks.  Un-chunked projections, one attention launch.  Same results as the NCCL paths (the kernels and
-        their order per token are the same)."""
+        their order per token are the same).  Three phases (produce, attend, project) separated by the barriers; they
+        are methods of their own so that a test can drive several emulated ranks through them on one GPU."""
+        c = self._peer_produce(attn, x, cos, sin, prequant, peers)
+        self._peer_attend(c, peers)
+        return self._peer_project(attn, c, peers, resid, gate)
+
+    def _peer_produce(self, attn, x: torch.Tensor, cos, sin, prequant, peers: PeerBuffers):
+        """Phase 1: project Q, K, V of this rank's tokens and send every head group to the rank that owns it."""
         s, D = x.shape
         H = attn.heads
         dev, dt = x.device, x.dtype
@@ -423,6 +431,15 @@ class DAXWanAttnProcessor2_0:
             if i == 1:
                 kv_sent = side.record_event()
 
+        return SimpleNamespace(s=s, D=D, P=P, rank=rank, h=h, hd=hd, S=S, esz=esz, dt=dt, dev=dev, recv=recv, o_recv=o_recv,
+                               o_ptrs=o_ptrs, main=main, side=side, kv_sent=kv_sent)
+
+    def _peer_attend(self, c, peers: PeerBuffers) -> None:
+        """Phase 2: once every rank's rows have landed, attention over the full sequence of this rank's heads; every
+        result row is stored into the buffer of the rank that owns the token."""
+        s, P, rank, h, hd, S, esz, dt = c.s, c.P, c.rank, c.h, c.hd, c.S, c.esz, c.dt
+        recv, o_ptrs, main, side, kv_sent = c.recv, c.o_ptrs, c.main, c.side, c.kv_sent
+
         def bhsd(t):
             return t.view(1, S, h, HEAD_DIM).transpose(1, 2)
 
@@ -445,6 +462,10 @@ class DAXWanAttnProcessor2_0:
             peers.barrier(2)  # ... and every rank's Q rows
             plan = ops.attn_prepare(*args, parts="q")
             ops.attn_forward_scatter(plan, o_dests, rows_per_dest=s, head_stride=HEAD_DIM, token_stride=hd)
+
+    def _peer_project(self, attn, c, peers: PeerBuffers, resid, gate) -> torch.Tensor:
+        """Phase 3: once every rank's attention rows for this rank's tokens have landed, the O projection."""
+        s, D, P, hd, dt, dev, o_recv = c.s, c.D, c.P, c.hd, c.dt, c.dev, c.o_recv
         peers.barrier(1)  # every rank's attention rows for my tokens have landed
         out = torch.empty((s, D), dtype=dt, device=dev)
         self._o_project(attn.to_out[0], (_Done(), o_recv, 0, s), out, P, hd, D, resid, gate)
