@@ -70,13 +70,27 @@ class PeerBuffers:
         self._any_handle.barrier(channel=channel, timeout_ms=self.BARRIER_TIMEOUT_MS)
 
 
-_PEERS: Dict[int, PeerBuffers] = {}
+_PEERS: Dict[int, Optional[PeerBuffers]] = {}
 
 
 def shared_peer_buffers(group, size: int, rank: int) -> Optional[PeerBuffers]:
-    if not PeerBuffers.supported():
-        return None
-    pb = _PEERS.get(id(group))
-    if pb is None:
-        pb = _PEERS[id(group)] = PeerBuffers(group, size, rank)
-    return pb
+    """The peer buffers of a group, or None where they cannot be had.  The first call per group is collective: every
+    rank tries a small symmetric allocation and the ranks agree (all-reduce of a flag) on whether ALL of them
+    succeeded, so that no rank takes the peer path while another falls back to NCCL."""
+    if id(group) in _PEERS:
+        return _PEERS[id(group)]
+    pb = None
+    ok = 0
+    if PeerBuffers.supported():
+        try:
+            pb = PeerBuffers(group, size, rank)
+            pb.get("probe", (256,), torch.float32, torch.device("cuda", torch.cuda.current_device()))
+            ok = 1
+        except Exception:
+            ok = 0
+    import torch.distributed as dist
+    flag = torch.tensor([ok], device="cuda" if torch.cuda.is_available() else "cpu", dtype=torch.int32)
+    if group is not None and size > 1 and dist.is_initialized():
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    _PEERS[id(group)] = pb if int(flag.item()) == 1 else None
+    return _PEERS[id(group)]
