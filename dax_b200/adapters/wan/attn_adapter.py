@@ -79,14 +79,15 @@ def _rope_tables(rotary_emb: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return cos, sin
 
 
-_SIDE_STREAMS: Dict[str, torch.cuda.Stream] = {}
+_SIDE_STREAMS: Dict[Tuple, torch.cuda.Stream] = {}
 
 
-def _side_stream(device) -> torch.cuda.Stream:
-    """The stream the copy engines' transfers are queued on (one per device)."""
-    st = _SIDE_STREAMS.get(str(device))
+def _side_stream(device, k: int = 0) -> torch.cuda.Stream:
+    """Stream `k` of the copy engines' transfers (a few per device, so that slabs for different destinations travel
+    at the same time)."""
+    st = _SIDE_STREAMS.get((str(device), k))
     if st is None:
-        st = _SIDE_STREAMS[str(device)] = torch.cuda.Stream(device=device)
+        st = _SIDE_STREAMS[(str(device), k)] = torch.cuda.Stream(device=device)
     return st
 
 
@@ -397,15 +398,20 @@ class DAXWanAttnProcessor2_0:
         # while the next projection runs on the SMs (a kernel that stored to the peers itself would be held to the
         # NVLink rate: these kernels are memory-bound or write short row segments).  V goes first, then K, then Q.
         main = torch.cuda.current_stream()
-        side = _side_stream(dev)
+        sides = [_side_stream(dev, k) for k in range(min(P - 1, 4))]
+        side = sides[0]
         send = [_BUFFERS.get(f"send{i}", (P, s, hd), dt, dev) for i in range(3)]
         kv_sent = None
+        # row chunks of the last projection: about five full waves of GEMM tiles each (128 x 256 tiles, one CTA per SM)
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        rows_target = 128 * max(1, round(5 * sms / ((D + 255) // 256)))
+        q_chunks = max(1, round(s / rows_target))
         for i in (2, 1, 0):
             lin, norm = lins[i], norms[i]
             plain = norm is None and (i == 2 or cos is None)
-            # the last tensor (Q) is projected in two row halves, so that only the second half's transfer (a sixth of
-            # the layer's Q/K/V bytes) is still in flight when the attention could start
-            bounds = chunk_bounds(s, 2) if (i == 0 and self._direct(dt, S, S)) else [0, s]
+            # the last tensor (Q) is projected in row chunks, so that only the last chunk's transfer is still in flight
+            # when the attention could start
+            bounds = chunk_bounds(s, q_chunks) if (i == 0 and self._direct(dt, S, S)) else [0, s]
             for c0, c1 in zip(bounds[:-1], bounds[1:]):
                 own = recv[i, rank * s + c0:rank * s + c1]
                 groups = [own.data_ptr() if p == rank else send[i][p, c0:c1].data_ptr() for p in range(P)]
@@ -423,22 +429,30 @@ class DAXWanAttnProcessor2_0:
                                           do_norm=norm is not None, eps=getattr(norm, "eps", 1e-6) if norm is not None else 1e-6,
                                           rope_cos=cos if rope else None, rope_sin=sin if rope else None,
                                           token_offset=rank * s + c0, row_sumsq=ss, ldo=hd, col_group=hd, group_ptrs=groups)
-                side.wait_stream(main)
+                for st in sides:
+                    st.wait_stream(main)
                 for dp in range(1, P):
                     p = (rank + dp) % P  # every rank starts with a different destination
                     # rank p owns head group p: my rows of tensor i land at rows [rank * s, (rank + 1) * s) of ITS buffer
-                    ops.peer_copy(recv_ptrs[p] + ((i * S + rank * s + c0) * hd) * esz, send[i][p, c0:c1], stream=side)
+                    ops.peer_copy(recv_ptrs[p] + ((i * S + rank * s + c0) * hd) * esz, send[i][p, c0:c1],
+                                  stream=sides[(dp - 1) % len(sides)])
             if i == 1:
+                for st in sides[1:]:
+                    side.wait_stream(st)
                 kv_sent = side.record_event()
 
         return SimpleNamespace(s=s, D=D, P=P, rank=rank, h=h, hd=hd, S=S, esz=esz, dt=dt, dev=dev, recv=recv, o_recv=o_recv,
-                               o_ptrs=o_ptrs, main=main, side=side, kv_sent=kv_sent)
+                               o_ptrs=o_ptrs, main=main, side=side, sides=sides, kv_sent=kv_sent)
 
     def _peer_attend(self, c, peers: PeerBuffers) -> None:
         """Phase 2: once every rank's rows have landed, attention over the full sequence of this rank's heads; every
         result row is stored into the buffer of the rank that owns the token."""
         s, P, rank, h, hd, S, esz, dt = c.s, c.P, c.rank, c.h, c.hd, c.S, c.esz, c.dt
         recv, o_ptrs, main, side, kv_sent = c.recv, c.o_ptrs, c.main, c.side, c.kv_sent
+
+        def wait_all_sent():
+            for st in c.sides:
+                main.wait_stream(st)
 
         def bhsd(t):
             return t.view(1, S, h, HEAD_DIM).transpose(1, 2)
@@ -447,7 +461,7 @@ class DAXWanAttnProcessor2_0:
         o_dests = [o_ptrs[d] + (rank * s * hd) * esz for d in range(P)]
         if self._direct(dt, S, S):
             # the 16-bit kernel reads Q, K, V where they landed: nothing to prepare
-            main.wait_stream(side)
+            wait_all_sent()
             peers.barrier(0)  # every rank's Q, K and V rows are in my buffers
             ops.attention_direct(bhsd(recv[0]), bhsd(recv[1]), bhsd(recv[2]), sm_scale=1.0 / math.sqrt(HEAD_DIM),
                                  dest_ptrs=o_dests, rows_per_dest=s, head_stride=HEAD_DIM, token_stride=hd)
@@ -458,7 +472,7 @@ class DAXWanAttnProcessor2_0:
             peers.barrier(0)  # every rank's K and V rows are in my buffers
             args = (bhsd(recv[0]), bhsd(recv[1]), bhsd(recv[2]), self.attention_mode, 1.0 / math.sqrt(HEAD_DIM))
             ops.attn_prepare(*args, parts="kv")
-            main.wait_stream(side)
+            wait_all_sent()
             peers.barrier(2)  # ... and every rank's Q rows
             plan = ops.attn_prepare(*args, parts="q")
             ops.attn_forward_scatter(plan, o_dests, rows_per_dest=s, head_stride=HEAD_DIM, token_stride=hd)
