@@ -148,20 +148,176 @@ ln_modulate_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D
       unpack2<BF16>(amax2, alo, ahi);
       const float amax = warp_max(fmaxf(alo, ahi));
       const float s = quant_scale<QDT>(amax, [](float v) { return to_f<BF16>(from_f<BF16>(v)); });
-      const float inv = __fdiv_rn(1.0f, s);
+      const float inv = quant_inv_scale(s);
       if (lane == 0) qscale[t] = s;
+      const uint64_t neg_s2 = f2_splat(-s), inv2 = f2_splat(inv);
 #pragma unroll
       for (int i = 0; i < NV; ++i)
         if (lane + 32 * i < nvec) {
-          float f[8];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) unpack2<BF16>(raw[i].w[k], f[2 * k], f[2 * k + 1]);
-          const uint32_t w0 = quant_four<QDT>(f[0], f[1], f[2], f[3], s, inv);
-          const uint32_t w1 = quant_four<QDT>(f[4], f[5], f[6], f[7], s, inv);
+          const uint32_t w0 = quant_four16<BF16, QDT>(raw[i].w[0], raw[i].w[1], neg_s2, inv2);
+          const uint32_t w1 = quant_four16<BF16, QDT>(raw[i].w[2], raw[i].w[3], neg_s2, inv2);
           *reinterpret_cast<uint2*>(q + t * D + static_cast<int64_t>(lane + 32 * i) * 8) = make_uint2(w0, w1);
         }
     }
   }
+}
+
+// ---- rows that fill a CTA exactly: one CTA per row, T threads x NV vectors = D / 8 --------------------------------
+// Bound by instruction issue before HBM, so the design counts instructions.  The rows travel through a ring of kRing
+// rows in shared memory, each thread copying (cp.async) and reading back its own 16-byte pieces: the bytes in flight
+// cost neither registers nor barriers.  A row is widened to fp32 once and stays in registers through the four steps
+// (sum, centred sum of squares, normalise + round + absmax, quantise); the arithmetic runs on fp32 pairs.  Few
+// threads per row (4-6 warps, 32-40 elements per thread) keep the per-row cost of the three CTA-wide reductions and
+// of the scale small per element; several CTAs per SM hide one another's barriers.  The per-column coefficients are
+// read from global memory for every row (they stay in L1: the rows themselves bypass it).
+constexpr int kRing = 3;
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
+               "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// acc = max(|acc|, |w|) per half, sign bits left undefined (the caller clears them at the end): one instruction
+template <bool BF16>
+__device__ __forceinline__ uint32_t absmax2_lazy(uint32_t acc, uint32_t w) {
+  uint32_t r;
+  if constexpr (BF16) asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(acc), "r"(w));
+  else asm("max.xorsign.abs.f16x2 %0, %1, %2;" : "=r"(r) : "r"(acc), "r"(w));
+  return r;
+}
+
+template <bool BF16, int QDT, int T, int NV, int MINB>
+__global__ void __launch_bounds__(T, MINB)
+ln_rows_cta_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D, int64_t ldx, const float* __restrict__ w,
+                   const float* __restrict__ b, const float* __restrict__ shift, const float* __restrict__ scale,
+                   float eps, uint16_t* __restrict__ y, int64_t ldy, uint8_t* __restrict__ q, float* __restrict__ qscale) {
+  constexpr int kWarps = T / 32;
+  extern __shared__ __align__(16) uint8_t ring_raw[];
+  V8* ring = reinterpret_cast<V8*>(ring_raw);  // [kRing][NV][T]
+  __shared__ __align__(16) float red[3][2][8];
+  static_assert(kWarps <= 8, "the reduction buffers hold eight warps");
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  auto fetch_row = [&](int64_t row, int slot) {
+    if (row < rows) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) cp_async16(ring + (slot * NV + i) * T + tid, x + row * ldx + static_cast<int64_t>(tid + i * T) * 8);
+    }
+    cp_async_commit();  // one group per row, empty past the end, so that the group count stays uniform
+  };
+  // CTA-wide sum or maximum; two result buffers per reduction, so one barrier is enough
+  auto cta_reduce = [&](float v, int which, int it, bool is_max) -> float {
+    v = is_max ? warp_max(v) : warp_sum(v);
+    float* r = red[which][it & 1];
+    if (lane == 0) r[warp] = v;
+    __syncthreads();
+    const float4 p0 = *reinterpret_cast<const float4*>(r);
+    float acc = p0.x;
+    const float e[8] = {p0.x, p0.y, p0.z, p0.w, 0.f, 0.f, 0.f, 0.f};
+    float4 p1 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (kWarps > 4) p1 = *reinterpret_cast<const float4*>(r + 4);
+    const float e1[4] = {p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+    for (int k = 1; k < kWarps; ++k) {
+      const float u = k < 4 ? e[k] : e1[k - 4];
+      acc = is_max ? fmaxf(acc, u) : acc + u;
+    }
+    return acc;
+  };
+
+  const float inv_d = 1.f / static_cast<float>(D);
+  const uint64_t one2 = f2_splat(1.f);
+  int64_t t = blockIdx.x;
+  const int64_t step = gridDim.x;
+#pragma unroll
+  for (int k = 0; k < kRing - 1; ++k) fetch_row(t + k * step, k);
+  for (int it = 0; t < rows; t += step, ++it) {
+    fetch_row(t + (kRing - 1) * step, (it + kRing - 1) % kRing);
+    cp_async_wait<kRing - 1>();  // this thread's pieces of row t have landed
+    uint64_t f[NV][4];
+    uint64_t acc = f2_splat(0.f);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const V8 raw = ring[((it % kRing) * NV + i) * T + tid];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        f[i][k] = f2_from16<BF16>(raw.w[k]);
+        acc = f2_add(acc, f[i][k]);
+      }
+    }
+    float lo, hi;
+    f2_unpack(acc, lo, hi);
+    const float mean = cta_reduce(lo + hi, 0, it, false) * inv_d;
+    const uint64_t neg_mean2 = f2_splat(-mean);
+    acc = f2_splat(0.f);
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        f[i][k] = f2_add(f[i][k], neg_mean2);
+        acc = f2_fma(f[i][k], f[i][k], acc);
+      }
+    f2_unpack(acc, lo, hi);
+    const uint64_t rstd2 = f2_splat(rsqrtf(cta_reduce(lo + hi, 1, it, false) * inv_d + eps));
+    uint32_t amax2 = 0u;
+    V8 out[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int64_t n = static_cast<int64_t>(tid + i * T) * 8;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {  // four columns at a time
+        uint64_t v0 = f2_mul(f[i][2 * h], rstd2), v1 = f2_mul(f[i][2 * h + 1], rstd2);
+        if (w != nullptr) {
+          const float4 m = __ldg(reinterpret_cast<const float4*>(w + n + 4 * h));
+          const float4 a = b != nullptr ? __ldg(reinterpret_cast<const float4*>(b + n + 4 * h)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          v0 = f2_fma(v0, f2_pack(m.x, m.y), f2_pack(a.x, a.y));
+          v1 = f2_fma(v1, f2_pack(m.z, m.w), f2_pack(a.z, a.w));
+        }
+        if (scale != nullptr) {
+          const float4 m = __ldg(reinterpret_cast<const float4*>(scale + n + 4 * h));
+          const float4 a = __ldg(reinterpret_cast<const float4*>(shift + n + 4 * h));
+          v0 = f2_fma(v0, f2_add(f2_pack(m.x, m.y), one2), f2_pack(a.x, a.y));
+          v1 = f2_fma(v1, f2_add(f2_pack(m.z, m.w), one2), f2_pack(a.z, a.w));
+        }
+        // the tensor the reference materialises in the activation dtype
+        out[i].w[2 * h] = f2_to16_rn<BF16>(v0);
+        out[i].w[2 * h + 1] = f2_to16_rn<BF16>(v1);
+        amax2 = absmax2_lazy<BF16>(absmax2_lazy<BF16>(amax2, out[i].w[2 * h]), out[i].w[2 * h + 1]);
+      }
+      if (y != nullptr) *reinterpret_cast<V8*>(y + t * ldy + n) = out[i];
+    }
+    if constexpr (QDT >= 0) {
+      float alo, ahi;
+      unpack2<BF16>(amax2 & 0x7fff7fffu, alo, ahi);
+      const float amax = cta_reduce(fmaxf(alo, ahi), 2, it, true);
+      const float s = quant_scale<QDT>(amax, [](float v) { return to_f<BF16>(from_f<BF16>(v)); });
+      const float inv = quant_inv_scale(s);
+      if (tid == 0) qscale[t] = s;
+      const uint64_t neg_s2 = f2_splat(-s), inv2 = f2_splat(inv);
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const uint32_t c0 = quant_four16<BF16, QDT>(out[i].w[0], out[i].w[1], neg_s2, inv2);
+        const uint32_t c1 = quant_four16<BF16, QDT>(out[i].w[2], out[i].w[3], neg_s2, inv2);
+        *reinterpret_cast<uint2*>(q + t * D + static_cast<int64_t>(tid + i * T) * 8) = make_uint2(c0, c1);
+      }
+    }
+  }
+}
+
+template <bool BF16, int QDT, int T, int NV, int MINB>
+int launch_cta_rows(int64_t s, cudaStream_t st, const uint16_t* x, int64_t D, int64_t ldx, const float* w, const float* b,
+                    const float* shift, const float* scale, float eps, uint16_t* y, int64_t ldy, uint8_t* q, float* qscale) {
+  int per_sm = 0;
+  constexpr size_t smem = static_cast<size_t>(kRing) * NV * T * sizeof(V8);
+  static_assert(smem <= 48 * 1024, "the ring fits the default dynamic shared memory limit");
+  DAX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ln_rows_cta_kernel<BF16, QDT, T, NV, MINB>, T, smem));
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>(s, static_cast<int64_t>(sm_count()) * std::max(per_sm, 1)));
+  ln_rows_cta_kernel<BF16, QDT, T, NV, MINB><<<grid, T, smem, st>>>(x, s, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
+  DAX_CUDA(cudaGetLastError());
+  return DAX_OK;
 }
 
 template <bool BF16, int QDT, int NV>
@@ -185,6 +341,17 @@ int launch(int64_t s, cudaStream_t st, const uint16_t* x, int64_t D, int64_t ldx
 template <bool BF16, int QDT>
 int dispatch_nv(int64_t s, cudaStream_t st, const uint16_t* x, int64_t D, int64_t ldx, const float* w, const float* b,
                 const float* shift, const float* scale, float eps, uint16_t* y, int64_t ldy, uint8_t* q, float* qscale) {
+  // rows that fill a CTA exactly take the CTA-per-row kernel (5120 = 160 threads x 4 vectors x 8)
+#define DAX_LN_CTA(T, NV, MINB) \
+  if (D == 8 * (T) * (NV)) \
+  return launch_cta_rows<BF16, QDT, T, NV, MINB>(s, st, x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale)
+  DAX_LN_CTA(160, 4, 4);   // 5120
+  DAX_LN_CTA(128, 4, 5);   // 4096
+  DAX_LN_CTA(128, 3, 6);   // 3072
+  DAX_LN_CTA(128, 2, 6);   // 2048
+  DAX_LN_CTA(96, 2, 8);    // 1536
+  DAX_LN_CTA(128, 1, 8);   // 1024
+#undef DAX_LN_CTA
   const int64_t nv = (D / 8 + 31) / 32;
 #define DAX_LN_CASE(N) if (nv <= N) return launch<BF16, QDT, N>(s, st, x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale)
   DAX_LN_CASE(1);

@@ -79,11 +79,9 @@ template <typename T, int QDT>
 __device__ __forceinline__ void emit_vec(const Vec<T>& t, float s, float inv, uint8_t* dst) {
   using V = VecTraits<T>;
   if constexpr (V::IS16) {
-    float f[8];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) unpack2<V::BF16>(t.w[k], f[2 * k], f[2 * k + 1]);
-    const uint32_t w0 = quant_four<QDT>(f[0], f[1], f[2], f[3], s, inv);
-    const uint32_t w1 = quant_four<QDT>(f[4], f[5], f[6], f[7], s, inv);
+    const uint64_t neg_s2 = f2_splat(-s), inv2 = f2_splat(inv);
+    const uint32_t w0 = quant_four16<V::BF16, QDT>(t.w[0], t.w[1], neg_s2, inv2);
+    const uint32_t w1 = quant_four16<V::BF16, QDT>(t.w[2], t.w[3], neg_s2, inv2);
     *reinterpret_cast<uint2*>(dst) = make_uint2(w0, w1);
   } else {
     *reinterpret_cast<uint32_t*>(dst) = quant_four<QDT>(__uint_as_float(t.w[0]), __uint_as_float(t.w[1]),
@@ -104,7 +102,6 @@ quant_rowwise_kernel(const T* __restrict__ x, int64_t M, int64_t K, int64_t ldx,
                      int64_t group_stride, uint8_t* __restrict__ q, float* __restrict__ scale) {
   constexpr int N = VecTraits<T>::N;
   constexpr int RPB = kThreads / TPR;
-  constexpr float qmax = QDT == DAX_I8 ? 127.f : (QDT == DAX_E4M3 ? 448.f : 57344.f);
   __shared__ float red[kThreads / 32];
 
   const int tid = threadIdx.x;
@@ -147,9 +144,8 @@ quant_rowwise_kernel(const T* __restrict__ x, int64_t M, int64_t K, int64_t ldx,
   }
   if (!live) return;
 
-  float s = VecTraits<T>::round_trip(__fdiv_rn(amax, qmax));
-  s = fmaxf(s, 1.1920928955078125e-07f);
-  const float inv = __fdiv_rn(1.0f, s);
+  const float s = quant_scale<QDT>(amax, [](float v) { return VecTraits<T>::round_trip(v); });
+  const float inv = quant_inv_scale(s);
   if (sub == 0) scale[row] = s;
 
   uint8_t* qrow = q + row * K;
@@ -175,7 +171,6 @@ __global__ void __launch_bounds__(kThreads)
 quant_rows_pipelined_kernel(const T* __restrict__ x, int64_t M, int64_t K, int64_t ldx, int64_t col_group,
                             int64_t group_stride, uint8_t* __restrict__ q, float* __restrict__ scale) {
   constexpr int N = VecTraits<T>::N;
-  constexpr float qmax = QDT == DAX_I8 ? 127.f : (QDT == DAX_E4M3 ? 448.f : 57344.f);
   __shared__ float red[2][kThreads / 32];
   const int tid = threadIdx.x;
   const int nvec = static_cast<int>(K / N);
@@ -209,9 +204,8 @@ quant_rows_pipelined_kernel(const T* __restrict__ x, int64_t M, int64_t K, int64
     amax = r[0];
 #pragma unroll
     for (int w = 1; w < kThreads / 32; ++w) amax = fmaxf(amax, r[w]);
-    float s = VecTraits<T>::round_trip(__fdiv_rn(amax, qmax));
-    s = fmaxf(s, 1.1920928955078125e-07f);
-    const float inv = __fdiv_rn(1.0f, s);
+    const float s = quant_scale<QDT>(amax, [](float v) { return VecTraits<T>::round_trip(v); });
+    const float inv = quant_inv_scale(s);
     if (tid == 0) scale[row] = s;
     uint8_t* qrow = q + row * K;
 #pragma unroll

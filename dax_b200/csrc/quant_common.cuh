@@ -81,15 +81,105 @@ __device__ __forceinline__ uint32_t quant_four(float a, float b, float c, float 
   }
 }
 
+// ---- packed fp32 pairs (one 64-bit register, two lanes of arithmetic per instruction) ----------------------
+// The row kernels are bound by instruction issue before they are bound by HBM; add / mul / fma on pairs halve
+// the arithmetic instructions.  Each lane of a pair is rounded exactly like the scalar instruction.
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t p, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(p));
+}
+__device__ __forceinline__ uint64_t f2_splat(float v) { return f2_pack(v, v); }
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+template <bool BF16>
+__device__ __forceinline__ uint64_t f2_from16(uint32_t w) {  // two 16-bit floats -> pair
+  float lo, hi;
+  unpack2<BF16>(w, lo, hi);
+  return f2_pack(lo, hi);
+}
+template <bool BF16>
+__device__ __forceinline__ uint32_t f2_to16_rn(uint64_t p) {
+  float lo, hi;
+  f2_unpack(p, lo, hi);
+  return pack2_rn<BF16>(lo, hi);
+}
+
+// Four 16-bit values (two packed words, element 0 in the low half of w0) -> four codes, the arithmetic of
+// quant_four on pairs: for FP8 the quotient is q0 = RN(x r) corrected once, e = x - q0 s, q = q0 + e r, and the
+// sign of x is put back on the CODE (the correction alone turns -0 into +0): the high byte of each 16-bit input
+// carries its sign, one byte permute collects the four of them.
+template <bool BF16, int QDT>
+__device__ __forceinline__ uint32_t quant_four16(uint32_t w0, uint32_t w1, uint64_t neg_scale2, uint64_t inv2) {
+  const uint64_t x0 = f2_from16<BF16>(w0), x1 = f2_from16<BF16>(w1);
+  if constexpr (QDT == DAX_I8) {
+    float a, b, c, d;
+    f2_unpack(f2_mul(x0, inv2), a, b);
+    f2_unpack(f2_mul(x1, inv2), c, d);
+    int32_t qa, qb, qc, qd;
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(qa) : "f"(a));
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(qb) : "f"(b));
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(qc) : "f"(c));
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(qd) : "f"(d));
+    uint32_t lo, hi, w;
+    asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(lo) : "r"(qa), "r"(qb));
+    asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(hi) : "r"(qc), "r"(qd));
+    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(w) : "r"(lo), "r"(hi));
+    return w;
+  } else {
+    const uint64_t q0 = f2_mul(x0, inv2), q1 = f2_mul(x1, inv2);
+    float a, b, c, d;
+    f2_unpack(f2_fma(f2_fma(q0, neg_scale2, x0), inv2, q0), a, b);
+    f2_unpack(f2_fma(f2_fma(q1, neg_scale2, x1), inv2, q1), c, d);
+    uint16_t lo, hi;
+    if constexpr (QDT == DAX_E4M3) {
+      asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
+      asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
+    } else {
+      asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
+      asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
+    }
+    uint32_t codes, signs;
+    asm("mov.b32 %0, {%1, %2};" : "=r"(codes) : "h"(lo), "h"(hi));
+    asm("prmt.b32 %0, %1, %2, 0x7531;" : "=r"(signs) : "r"(w0), "r"(w1));  // the high byte of each input
+    return (codes & 0x7f7f7f7fu) | (signs & 0x80808080u);
+  }
+}
+
 template <int QDT>
 __device__ __forceinline__ constexpr float quant_max() {
   return QDT == DAX_I8 ? 127.f : (QDT == DAX_E4M3 ? 448.f : 57344.f);
 }
 
 // scale = round_to_input_dtype(amax / qmax), floored at fp32 eps; `round_trip` rounds to the input dtype
+// The quotient amax / qmax is correctly rounded either way; the short form (div_rn_by with the constant
+// reciprocal) is three instructions instead of a division routine that every thread of a row would run.  It is
+// exact wherever it stays in the normal range: above it (an infinite or NaN amax) the full division runs, below
+// it the result is under the floor anyway.
 template <int QDT, typename RoundTrip>
 __device__ __forceinline__ float quant_scale(float amax, RoundTrip round_trip) {
-  return fmaxf(round_trip(__fdiv_rn(amax, quant_max<QDT>())), 1.1920928955078125e-07f);
+  constexpr float qmax = quant_max<QDT>();
+  constexpr float rq = 1.0f / qmax;  // correctly rounded by the host compiler
+  const float quot = amax <= 3.0e38f ? div_rn_by(amax, qmax, rq) : __fdiv_rn(amax, qmax);
+  return fmaxf(round_trip(quot), 1.1920928955078125e-07f);
 }
+// 1 / scale, correctly rounded (the same value as a full division of 1.0f by scale)
+__device__ __forceinline__ float quant_inv_scale(float scale) { return __frcp_rn(scale); }
 
 }  // namespace dax
