@@ -2,10 +2,11 @@
 // attention: the normalised, modulated activations feed a quantised linear, so the kernel can emit the
 // INT8 / FP8 codes and scales directly and the separate quantiser pass (and its HBM round trip) goes away.
 //
-// HBM-bound: 2 bytes read per element, 2 written (bf16 output) and/or 1 written (codes).  One WARP owns a token
-// row: the row lives in the warp's registers (128-bit loads, all issued before the first use), mean, centred
-// variance and the absmax of the rounded outputs are warp shuffles, so no row ever waits at a CTA barrier and the
-// eight warps of a CTA (and the CTAs sharing an SM) hide one another's memory latency.
+// 2 bytes read per element, 2 written (16-bit output) and/or 1 written (codes).  Two kernels:
+//  - rows whose width fills a CTA exactly (the model widths: 5120, 4096, 3072, 2048, 1536, 1024): one CTA of a few
+//    warps per row, the row widened to fp32 once, arithmetic on fp32 pairs (ln_rows_cta_kernel below);
+//  - any other width: one WARP owns a row, which lives packed in the warp's registers; mean, centred variance and
+//    the absmax of the rounded outputs are warp shuffles (ln_modulate_quant_kernel).
 //   y = round_dtype( LN(x) [* w + b] [* (1 + scale) + shift] )          LN: eps inside the square root
 //   (q, s) = dynamic per-token quantisation of y, arithmetic of quant_common.cuh
 #include <algorithm>
@@ -189,7 +190,7 @@ __device__ __forceinline__ uint32_t absmax2_lazy(uint32_t acc, uint32_t w) {
   return r;
 }
 
-template <bool BF16, int QDT, int T, int NV, int MINB>
+template <bool BF16, int QDT, int T, int NV, int MINB, int CR>
 __global__ void __launch_bounds__(T, MINB)
 ln_rows_cta_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D, int64_t ldx, const float* __restrict__ w,
                    const float* __restrict__ b, const float* __restrict__ shift, const float* __restrict__ scale,
@@ -197,39 +198,68 @@ ln_rows_cta_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D, int6
   constexpr int kWarps = T / 32;
   extern __shared__ __align__(16) uint8_t ring_raw[];
   V8* ring = reinterpret_cast<V8*>(ring_raw);  // [kRing][NV][T]
-  __shared__ __align__(16) float red[3][2][8];
-  static_assert(kWarps <= 8, "the reduction buffers hold eight warps");
+  __shared__ float2 red2[2][2][kWarps];  // [moments | centred sum of squares][iteration parity][warp]
+  __shared__ uint32_t redm[2][kWarps];   // absmax, as bit patterns
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  // this thread's columns: vector i covers elements [8 (tid + i T), +8) of the row
+  const uint16_t* x_t = x + tid * 8;
+  uint16_t* y_t = y != nullptr ? y + tid * 8 : nullptr;
+  uint8_t* q_t = q != nullptr ? q + tid * 8 : nullptr;
+  const float* w_t = w != nullptr ? w + tid * 8 : nullptr;
+  const float* b_t = b != nullptr ? b + tid * 8 : nullptr;
+  const float* sc_t = scale != nullptr ? scale + tid * 8 : nullptr;
+  const float* sh_t = shift != nullptr ? shift + tid * 8 : nullptr;
+  V8* ring_t = ring + tid;
 
   auto fetch_row = [&](int64_t row, int slot) {
     if (row < rows) {
 #pragma unroll
-      for (int i = 0; i < NV; ++i) cp_async16(ring + (slot * NV + i) * T + tid, x + row * ldx + static_cast<int64_t>(tid + i * T) * 8);
+      for (int i = 0; i < NV; ++i) cp_async16(ring_t + (slot * NV + i) * T, x_t + row * ldx + i * T * 8);
     }
     cp_async_commit();  // one group per row, empty past the end, so that the group count stays uniform
   };
-  // CTA-wide sum or maximum; two result buffers per reduction, so one barrier is enough
-  auto cta_reduce = [&](float v, int which, int it, bool is_max) -> float {
-    v = is_max ? warp_max(v) : warp_sum(v);
-    float* r = red[which][it & 1];
-    if (lane == 0) r[warp] = v;
+  // CTA-wide sums of a pair of values; two result buffers, so one barrier is enough
+  auto cta_sum2 = [&](float& a, float& c, int which, int it) {
+    a = warp_sum(a);
+    c = warp_sum(c);
+    float2* r = red2[which][it & 1];
+    if (lane == 0) r[warp] = make_float2(a, c);
     __syncthreads();
-    const float4 p0 = *reinterpret_cast<const float4*>(r);
-    float acc = p0.x;
-    const float e[8] = {p0.x, p0.y, p0.z, p0.w, 0.f, 0.f, 0.f, 0.f};
-    float4 p1 = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (kWarps > 4) p1 = *reinterpret_cast<const float4*>(r + 4);
-    const float e1[4] = {p1.x, p1.y, p1.z, p1.w};
+    a = r[0].x;
+    c = r[0].y;
 #pragma unroll
     for (int k = 1; k < kWarps; ++k) {
-      const float u = k < 4 ? e[k] : e1[k - 4];
-      acc = is_max ? fmaxf(acc, u) : acc + u;
+      a += r[k].x;
+      c += r[k].y;
     }
-    return acc;
   };
 
   const float inv_d = 1.f / static_cast<float>(D);
   const uint64_t one2 = f2_splat(1.f);
+  // The coefficients of the thread's first CR vectors stay in registers for the whole kernel, folded into one
+  // multiplier and one addend per column: (n w + b) (1 + scale) + shift = n [w (1 + scale)] + [b (1 + scale) + shift].
+  // Reading all of them from L1 for every row would make the L1 data path the bound.
+  uint64_t mulc[CR > 0 ? CR : 1][4], addc[CR > 0 ? CR : 1][4];
+  const bool affine = w != nullptr || scale != nullptr;
+  if (affine) {
+#pragma unroll
+    for (int i = 0; i < CR; ++i)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float m[2], a[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int n = i * T * 8 + 2 * k + h;
+          const float w0 = w != nullptr ? w_t[n] : 1.f, b0 = (w != nullptr && b != nullptr) ? b_t[n] : 0.f;
+          const float m1 = scale != nullptr ? 1.f + sc_t[n] : 1.f, a1 = scale != nullptr ? sh_t[n] : 0.f;
+          m[h] = w0 * m1;
+          a[h] = fmaf(b0, m1, a1);
+        }
+        mulc[i][k] = f2_pack(m[0], m[1]);
+        addc[i][k] = f2_pack(a[0], a[1]);
+      }
+  }
   int64_t t = blockIdx.x;
   const int64_t step = gridDim.x;
 #pragma unroll
@@ -237,63 +267,90 @@ ln_rows_cta_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D, int6
   for (int it = 0; t < rows; t += step, ++it) {
     fetch_row(t + (kRing - 1) * step, (it + kRing - 1) % kRing);
     cp_async_wait<kRing - 1>();  // this thread's pieces of row t have landed
+    // both moments in one pass and one reduction
     uint64_t f[NV][4];
-    uint64_t acc = f2_splat(0.f);
+    uint64_t acc = f2_splat(0.f), acc_sq = f2_splat(0.f);
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-      const V8 raw = ring[((it % kRing) * NV + i) * T + tid];
+      const V8 raw = ring_t[((it % kRing) * NV + i) * T];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         f[i][k] = f2_from16<BF16>(raw.w[k]);
         acc = f2_add(acc, f[i][k]);
+        acc_sq = f2_fma(f[i][k], f[i][k], acc_sq);
       }
     }
-    float lo, hi;
+    float lo, hi, qlo, qhi;
     f2_unpack(acc, lo, hi);
-    const float mean = cta_reduce(lo + hi, 0, it, false) * inv_d;
-    const uint64_t neg_mean2 = f2_splat(-mean);
-    acc = f2_splat(0.f);
+    f2_unpack(acc_sq, qlo, qhi);
+    float sum = lo + hi, sumsq = qlo + qhi;
+    cta_sum2(sum, sumsq, 0, it);
+    const float mean = div_rn_by(sum, static_cast<float>(D), inv_d);  // the correctly rounded quotient: a constant row gives itself
+    float var = fmaf(-mean, mean, sumsq * inv_d);
+    // E[x^2] - mean^2 loses digits when the mean dwarfs the spread: such a row (every thread sees the same two
+    // numbers, so the branch is uniform) gets the centred sum of squares instead
+    if (!(var * 64.f > mean * mean)) {
+      const uint64_t neg_mean2 = f2_splat(-mean);
+      uint64_t c2 = f2_splat(0.f);
 #pragma unroll
-    for (int i = 0; i < NV; ++i)
+      for (int i = 0; i < NV; ++i)
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        f[i][k] = f2_add(f[i][k], neg_mean2);
-        acc = f2_fma(f[i][k], f[i][k], acc);
-      }
-    f2_unpack(acc, lo, hi);
-    const uint64_t rstd2 = f2_splat(rsqrtf(cta_reduce(lo + hi, 1, it, false) * inv_d + eps));
+        for (int k = 0; k < 4; ++k) {
+          const uint64_t dlt = f2_add(f[i][k], neg_mean2);
+          c2 = f2_fma(dlt, dlt, c2);
+        }
+      f2_unpack(c2, lo, hi);
+      float centred = lo + hi, unused = 0.f;
+      cta_sum2(centred, unused, 1, it);
+      var = centred * inv_d;
+    }
+    const float rstd = rsqrtf(var + eps);
+    const uint64_t rstd2 = f2_splat(rstd), shift2 = f2_splat(-mean * rstd);
     uint32_t amax2 = 0u;
     V8 out[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-      const int64_t n = static_cast<int64_t>(tid + i * T) * 8;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {  // four columns at a time
-        uint64_t v0 = f2_mul(f[i][2 * h], rstd2), v1 = f2_mul(f[i][2 * h + 1], rstd2);
+        uint64_t v0 = f2_fma(f[i][2 * h], rstd2, shift2), v1 = f2_fma(f[i][2 * h + 1], rstd2, shift2);
+        if (i < CR) {
+          if (affine) {
+            v0 = f2_fma(v0, mulc[i < CR ? i : 0][2 * h], addc[i < CR ? i : 0][2 * h]);
+            v1 = f2_fma(v1, mulc[i < CR ? i : 0][2 * h + 1], addc[i < CR ? i : 0][2 * h + 1]);
+          }
+        } else {
         if (w != nullptr) {
-          const float4 m = __ldg(reinterpret_cast<const float4*>(w + n + 4 * h));
-          const float4 a = b != nullptr ? __ldg(reinterpret_cast<const float4*>(b + n + 4 * h)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          const float4 m = __ldg(reinterpret_cast<const float4*>(w_t + i * T * 8 + 4 * h));
+          const float4 a = b != nullptr ? __ldg(reinterpret_cast<const float4*>(b_t + i * T * 8 + 4 * h)) : make_float4(0.f, 0.f, 0.f, 0.f);
           v0 = f2_fma(v0, f2_pack(m.x, m.y), f2_pack(a.x, a.y));
           v1 = f2_fma(v1, f2_pack(m.z, m.w), f2_pack(a.z, a.w));
         }
         if (scale != nullptr) {
-          const float4 m = __ldg(reinterpret_cast<const float4*>(scale + n + 4 * h));
-          const float4 a = __ldg(reinterpret_cast<const float4*>(shift + n + 4 * h));
+          const float4 m = __ldg(reinterpret_cast<const float4*>(sc_t + i * T * 8 + 4 * h));
+          const float4 a = __ldg(reinterpret_cast<const float4*>(sh_t + i * T * 8 + 4 * h));
           v0 = f2_fma(v0, f2_add(f2_pack(m.x, m.y), one2), f2_pack(a.x, a.y));
           v1 = f2_fma(v1, f2_add(f2_pack(m.z, m.w), one2), f2_pack(a.z, a.w));
+        }
         }
         // the tensor the reference materialises in the activation dtype
         out[i].w[2 * h] = f2_to16_rn<BF16>(v0);
         out[i].w[2 * h + 1] = f2_to16_rn<BF16>(v1);
         amax2 = absmax2_lazy<BF16>(absmax2_lazy<BF16>(amax2, out[i].w[2 * h]), out[i].w[2 * h + 1]);
       }
-      if (y != nullptr) *reinterpret_cast<V8*>(y + t * ldy + n) = out[i];
+      if (y != nullptr) *reinterpret_cast<V8*>(y_t + t * ldy + i * T * 8) = out[i];
     }
     if constexpr (QDT >= 0) {
+      // non-negative floats order like their bit patterns: the maximum is an integer reduction
       float alo, ahi;
       unpack2<BF16>(amax2 & 0x7fff7fffu, alo, ahi);
-      const float amax = cta_reduce(fmaxf(alo, ahi), 2, it, true);
-      const float s = quant_scale<QDT>(amax, [](float v) { return to_f<BF16>(from_f<BF16>(v)); });
+      const uint32_t wmax = __reduce_max_sync(0xffffffffu, __float_as_uint(fmaxf(alo, ahi)));
+      uint32_t* r = redm[it & 1];
+      if (lane == 0) r[warp] = wmax;
+      __syncthreads();
+      uint32_t cmax = r[0];
+#pragma unroll
+      for (int k = 1; k < kWarps; ++k) cmax = max(cmax, r[k]);
+      const float s = quant_scale<QDT>(__uint_as_float(cmax), [](float v) { return to_f<BF16>(from_f<BF16>(v)); });
       const float inv = quant_inv_scale(s);
       if (tid == 0) qscale[t] = s;
       const uint64_t neg_s2 = f2_splat(-s), inv2 = f2_splat(inv);
@@ -301,21 +358,21 @@ ln_rows_cta_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D, int6
       for (int i = 0; i < NV; ++i) {
         const uint32_t c0 = quant_four16<BF16, QDT>(out[i].w[0], out[i].w[1], neg_s2, inv2);
         const uint32_t c1 = quant_four16<BF16, QDT>(out[i].w[2], out[i].w[3], neg_s2, inv2);
-        *reinterpret_cast<uint2*>(q + t * D + static_cast<int64_t>(tid + i * T) * 8) = make_uint2(c0, c1);
+        *reinterpret_cast<uint2*>(q_t + t * D + i * T * 8) = make_uint2(c0, c1);
       }
     }
   }
 }
 
-template <bool BF16, int QDT, int T, int NV, int MINB>
+template <bool BF16, int QDT, int T, int NV, int MINB, int CR>
 int launch_cta_rows(int64_t s, cudaStream_t st, const uint16_t* x, int64_t D, int64_t ldx, const float* w, const float* b,
                     const float* shift, const float* scale, float eps, uint16_t* y, int64_t ldy, uint8_t* q, float* qscale) {
   int per_sm = 0;
   constexpr size_t smem = static_cast<size_t>(kRing) * NV * T * sizeof(V8);
   static_assert(smem <= 48 * 1024, "the ring fits the default dynamic shared memory limit");
-  DAX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ln_rows_cta_kernel<BF16, QDT, T, NV, MINB>, T, smem));
+  DAX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ln_rows_cta_kernel<BF16, QDT, T, NV, MINB, CR>, T, smem));
   const unsigned grid = static_cast<unsigned>(std::min<int64_t>(s, static_cast<int64_t>(sm_count()) * std::max(per_sm, 1)));
-  ln_rows_cta_kernel<BF16, QDT, T, NV, MINB><<<grid, T, smem, st>>>(x, s, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
+  ln_rows_cta_kernel<BF16, QDT, T, NV, MINB, CR><<<grid, T, smem, st>>>(x, s, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
   DAX_CUDA(cudaGetLastError());
   return DAX_OK;
 }
@@ -342,15 +399,15 @@ template <bool BF16, int QDT>
 int dispatch_nv(int64_t s, cudaStream_t st, const uint16_t* x, int64_t D, int64_t ldx, const float* w, const float* b,
                 const float* shift, const float* scale, float eps, uint16_t* y, int64_t ldy, uint8_t* q, float* qscale) {
   // rows that fill a CTA exactly take the CTA-per-row kernel (5120 = 160 threads x 4 vectors x 8)
-#define DAX_LN_CTA(T, NV, MINB) \
+#define DAX_LN_CTA(T, NV, MINB, CR) \
   if (D == 8 * (T) * (NV)) \
-  return launch_cta_rows<BF16, QDT, T, NV, MINB>(s, st, x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale)
-  DAX_LN_CTA(160, 4, 4);   // 5120
-  DAX_LN_CTA(128, 4, 5);   // 4096
-  DAX_LN_CTA(128, 3, 6);   // 3072
-  DAX_LN_CTA(128, 2, 6);   // 2048
-  DAX_LN_CTA(96, 2, 8);    // 1536
-  DAX_LN_CTA(128, 1, 8);   // 1024
+  return launch_cta_rows<BF16, QDT, T, NV, MINB, CR>(s, st, x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale)
+  DAX_LN_CTA(160, 4, 3, 2);   // 5120
+  DAX_LN_CTA(128, 4, 4, 2);   // 4096
+  DAX_LN_CTA(128, 3, 5, 2);   // 3072
+  DAX_LN_CTA(128, 2, 6, 2);   // 2048
+  DAX_LN_CTA(96, 2, 8, 2);    // 1536
+  DAX_LN_CTA(128, 1, 8, 1);   // 1024
 #undef DAX_LN_CTA
   const int64_t nv = (D / 8 + 31) / 32;
 #define DAX_LN_CASE(N) if (nv <= N) return launch<BF16, QDT, N>(s, st, x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale)

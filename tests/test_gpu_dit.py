@@ -63,6 +63,25 @@ def test_layernorm_modulate_quant_many_rows(ops):
         assert torch.equal(yi[0], y[i]) and torch.equal(qi[0], q[i]) and torch.equal(si[0], qs[i])
 
 
+@pytest.mark.parametrize("D", [5120, 1000 * 8])
+def test_layernorm_rows_with_a_large_mean(ops, D):
+    """Rows whose mean dwarfs their spread (E[x^2] - mean^2 would cancel) and a constant row: the centred form must
+    take over.  fp16 input, whose spacing near 100 is fine enough to carry a spread of 0.1.  Both kernels (a width
+    that fills a CTA exactly, and one that does not)."""
+    torch.manual_seed(21)
+    s = 37
+    x = (100.0 + 0.1 * torch.randn(s, D)).half()
+    x[5] = 3.0
+    x[6] = 0.0
+    ref = O.layernorm(x).half()
+    y, q, qs = ops.layernorm_modulate_quant(x.to(DEV), q_dtype=torch.int8)
+    assert torch.isfinite(y).all()
+    assert O.rel_l2(y.cpu(), ref) <= 3e-3
+    assert float(y[5].abs().max()) <= 1e-3 and float(y[6].abs().max()) == 0.0
+    qr, sr = O.quantize_rowwise(y.cpu(), torch.int8)
+    assert torch.equal(q.cpu(), qr) and torch.equal(qs.cpu(), sr)
+
+
 @pytest.mark.parametrize("wdt", [torch.int8, torch.float8_e4m3fn])
 def test_gemm_epilogues(ops, wdt):
     torch.manual_seed(3)
