@@ -20,7 +20,7 @@ def ops(built_library):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("D", [256, 1536, 5120])
+@pytest.mark.parametrize("D", [256, 1024, 1536, 2048, 3072, 4096, 5120, 6144])
 def test_layernorm_modulate_quant(ops, dtype, D):
     torch.manual_seed(D)
     s = 45

@@ -211,8 +211,8 @@ def test_gemm_full_size_linearity(ops):
 
 # ---- RMSNorm + RoPE + pack ---------------------------------------------------------------------------
 def test_rmsnorm_rope_pack_many_rows_full_width(ops):
-    """Production width (5120 = 40 heads, three vectors per thread, the third ragged) and more rows than resident
-    CTAs, so that every CTA strides over several rows with the next row's loads in flight."""
+    """Production width (5120 = 40 heads: 320 threads x 2 vectors) and more rows than resident CTAs, so that every
+    CTA strides over several rows with the next rows' copies in flight."""
     torch.manual_seed(5)
     grid = (3, 20, 25)
     S, H = 1500, 40
@@ -269,6 +269,29 @@ def test_rmsnorm_rope_pack(ops, dtype):
     assert O.rel_l2(y3.cpu(), ref3) <= 2e-3
     y4 = ops.rmsnorm_rope_pack(x.to(DEV), norm_weight=w.to(DEV), do_norm=True)
     assert O.rel_l2(y4.cpu(), O.rmsnorm(x, w)) <= 2e-3
+
+
+@pytest.mark.parametrize("H", [2, 16, 24, 32, 56, 64, 72])
+def test_rmsnorm_rope_pack_widths(ops, H):
+    """One width per kernel variant: rows that fill the CTA exactly (no predicates) and ragged ones, 1 to 4 vectors
+    per thread, and the widest CTA; more rows than the copy ring is deep."""
+    torch.manual_seed(H)
+    grid = (2, 5, 7)
+    S, D = 70, H * 128
+    x = torch.randn(S, D).bfloat16()
+    w = (1 + 0.1 * torch.randn(D)).bfloat16()
+    fr = O.rope_table(grid)
+    ref = O.rmsnorm(x.unsqueeze(0), w).unflatten(2, (H, -1)).transpose(1, 2)
+    ref = O.apply_rotary_emb(ref, fr).transpose(1, 2).flatten(2, 3)[0]
+    cos = fr.real.float().reshape(S, 64).contiguous().to(DEV)
+    sin = fr.imag.float().reshape(S, 64).contiguous().to(DEV)
+    y = ops.rmsnorm_rope_pack(x.to(DEV), norm_weight=w.to(DEV), do_norm=True, rope_cos=cos, rope_sin=sin)
+    assert O.rel_l2(y.cpu(), ref) <= 2e-3
+    # one partial sum per 128 columns, as the GEMM epilogue writes them (72 of them at the widest: more than two per lane)
+    parts = x.float().pow(2).view(S, H, 128).sum(-1)
+    y2 = ops.rmsnorm_rope_pack(x.to(DEV), norm_weight=w.to(DEV), do_norm=True, rope_cos=cos, rope_sin=sin,
+                               row_sumsq=parts.to(DEV))
+    assert O.rel_l2(y2.cpu(), ref) <= 2e-3
 
 
 # ---- attention ---------------------------------------------------------------------------------------
