@@ -398,7 +398,8 @@ int launch(int64_t s, cudaStream_t st, const uint16_t* x, int64_t D, int64_t ldx
 template <bool BF16, int QDT>
 int dispatch_nv(int64_t s, cudaStream_t st, const uint16_t* x, int64_t D, int64_t ldx, const float* w, const float* b,
                 const float* shift, const float* scale, float eps, uint16_t* y, int64_t ldy, uint8_t* q, float* qscale) {
-  // rows that fill a CTA exactly take the CTA-per-row kernel (5120 = 160 threads x 4 vectors x 8)
+  // rows that fill a CTA exactly take the CTA-per-row kernel (5120 = 160 threads x 4 vectors x 8); per width: threads,
+  // vectors per thread, CTAs per SM the register allocation is held to, vectors whose coefficients live in registers
 #define DAX_LN_CTA(T, NV, MINB, CR) \
   if (D == 8 * (T) * (NV)) \
   return launch_cta_rows<BF16, QDT, T, NV, MINB, CR>(s, st, x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale)
