@@ -146,8 +146,40 @@ def case_zero_copy_chunks(rank, world):
         assert torch.equal(slab.transpose(0, 1).reshape(1, s, H, d), O.collect_heads_ref(full, rank))
 
 
+def case_peer_probe_agrees(rank, world):
+    """The peer-buffer probe is collective: where one rank cannot have peer-mapped buffers, no rank takes the peer
+    path.  On CPU no rank can (the answer must still be the same everywhere); then rank 1 alone is made to 'succeed'
+    and the minimum over the ranks still says no."""
+    from dax_b200.parallel import peer
+    from dax_b200.parallel.dist import parallel_state as ps
+    group = ps.get_sequence_parallel_group()
+    assert peer.shared_peer_buffers(group, world, rank) is None
+    assert peer.shared_peer_buffers(group, world, rank) is None  # cached, no second collective
+    peer._PEERS.clear()
+
+    class FakeBuffers:
+        def __init__(self, group, size, rank):
+            self.P, self.rank = size, rank
+
+        @staticmethod
+        def supported():
+            return rank == 1
+
+        def get(self, *a, **k):
+            return None
+
+    real = peer.PeerBuffers
+    peer.PeerBuffers = FakeBuffers
+    try:
+        assert peer.shared_peer_buffers(group, world, rank) is None
+    finally:
+        peer.PeerBuffers = real
+        peer._PEERS.clear()
+
+
 @pytest.mark.parametrize("world", [2, 4])
-@pytest.mark.parametrize("case", ["case_state", "case_sync_exchange", "case_async_exchange", "case_zero_copy_chunks"])
+@pytest.mark.parametrize("case", ["case_state", "case_sync_exchange", "case_async_exchange", "case_zero_copy_chunks",
+                                  "case_peer_probe_agrees"])
 def test_gloo(case, world):
     run(case, world)
 
