@@ -47,7 +47,7 @@ __device__ __forceinline__ float warp_max(float v) {
 template <int NV> struct LnThreads { static constexpr int value = NV <= 12 ? 256 : 128; };
 
 template <bool BF16, int QDT, int NV>
-__global__ void __launch_bounds__(LnThreads<NV>::value, NV <= 8 ? 3 : (NV <= 12 ? 2 : 3))
+__global__ void __launch_bounds__(LnThreads<NV>::value, NV <= 6 ? 3 : (NV <= 12 ? 2 : (NV <= 24 ? 3 : 2)))
 ln_modulate_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D, int64_t ldx, const float* __restrict__ w,
                          const float* __restrict__ b, const float* __restrict__ shift,
                          const float* __restrict__ scale, float eps, uint16_t* __restrict__ y, int64_t ldy,
