@@ -3,7 +3,7 @@
 // HBM-bound: 2 (or 4) bytes read and 1 byte written per element plus 4 bytes per row.  A row is
 // read once with 128-bit loads into registers, reduced, and quantised from registers.  Short rows go one per
 // warp; rows of 257..2048 vectors go to CTAs that stride over the rows with the next row's loads already in
-// flight while the current row is reduced and converted (5.3-6.4 TB/s at 75,600 x 5120 / 13,824 on a B200);
+// flight while the current row is reduced and converted (6.6-6.7 TB/s at 75,600 x 5120 / 13,824 on a B200);
 // longer rows are re-read from L2 for the second pass.
 //
 // Arithmetic follows the reference bit for bit (dax/quant/nn/dynamic/functional.py:124-135 and
@@ -12,8 +12,8 @@
 //   scale = round_to_input_dtype(amax / qmax), floored at fp32 eps, widened to fp32
 //   INT8: q = clamp(rint(x * (1.0f / scale)), -128, 127)    (multiply by the reciprocal)
 //   FP8 : q = round_nearest_even_to_fp8(clamp(x / scale))   (true division, see div_rn_by)
-// All fp32 operations are the IEEE round-to-nearest intrinsics so that the compiler cannot
-// contract or approximate them.
+// All fp32 operations are IEEE round-to-nearest (intrinsics, or the packed-pair instructions of quant_common.cuh,
+// whose lanes round like the scalar ones) so that the compiler cannot contract or approximate them.
 #include <algorithm>
 
 #include "quant_common.cuh"

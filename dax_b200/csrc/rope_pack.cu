@@ -2,8 +2,9 @@
 // one pass over HBM (2 bytes read + 2 bytes written per element; the rotary tables and the norm
 // weight stay in L2).
 //
-// CTAs stride over the token rows.  A row is read once into registers with 128-bit loads, and the next
-// row's loads are issued before the current row is normalised and rotated.  The sum of
+// CTAs stride over the token rows.  A row is read once: it travels through a ring of rows in shared memory
+// (cp.async, 16 bytes per thread and vector; every thread reads back only what it copied itself, so no barrier
+// is involved) with the next rows' copies in flight while the current row is normalised and rotated.  The sum of
 // squares either comes from the per-column-tile partial sums the projection GEMM's epilogue wrote
 // (summed in tile order, so the result does not depend on scheduling) or is reduced here.
 // The normalised value is rounded to the tensor dtype before the rotation, like the tensor the
