@@ -171,7 +171,7 @@ ln_modulate_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D
 // threads per row (4-6 warps, 32-40 elements per thread) keep the per-row cost of the three CTA-wide reductions and
 // of the scale small per element; several CTAs per SM hide one another's barriers.  The per-column coefficients are
 // read from global memory for every row (they stay in L1: the rows themselves bypass it).
-constexpr int kRing = 3;
+constexpr int kRing = 2;
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
@@ -198,6 +198,7 @@ ln_rows_cta_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D, int6
   constexpr int kWarps = T / 32;
   extern __shared__ __align__(16) uint8_t ring_raw[];
   V8* ring = reinterpret_cast<V8*>(ring_raw);  // [kRing][NV][T]
+  float4* coef = reinterpret_cast<float4*>(ring_raw + sizeof(V8) * kRing * NV * T) + threadIdx.x;  // [NV - CR][4][T]
   __shared__ float2 red2[2][2][kWarps];  // [moments | centred sum of squares][iteration parity][warp]
   __shared__ uint32_t redm[2][kWarps];   // absmax, as bit patterns
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -236,29 +237,38 @@ ln_rows_cta_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D, int6
   };
 
   const float inv_d = 1.f / static_cast<float>(D);
-  const uint64_t one2 = f2_splat(1.f);
-  // The coefficients of the thread's first CR vectors stay in registers for the whole kernel, folded into one
-  // multiplier and one addend per column: (n w + b) (1 + scale) + shift = n [w (1 + scale)] + [b (1 + scale) + shift].
-  // Reading all of them from L1 for every row would make the L1 data path the bound.
+  // Per-column coefficients, folded into one multiplier and one addend per column:
+  // (n w + b) (1 + scale) + shift = n [w (1 + scale)] + [b (1 + scale) + shift].  Those of the thread's first CR
+  // vectors stay in registers for the whole kernel, the others in shared memory (read back once per row): reading
+  // all of them through the L1 / shared-memory data path for every row would make that path the bound.
   uint64_t mulc[CR > 0 ? CR : 1][4], addc[CR > 0 ? CR : 1][4];
   const bool affine = w != nullptr || scale != nullptr;
   if (affine) {
 #pragma unroll
-    for (int i = 0; i < CR; ++i)
+    for (int i = 0; i < NV; ++i) {
+      float m[8], a[8];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        float m[2], a[2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int n = i * T * 8 + 2 * k + h;
-          const float w0 = w != nullptr ? w_t[n] : 1.f, b0 = (w != nullptr && b != nullptr) ? b_t[n] : 0.f;
-          const float m1 = scale != nullptr ? 1.f + sc_t[n] : 1.f, a1 = scale != nullptr ? sh_t[n] : 0.f;
-          m[h] = w0 * m1;
-          a[h] = fmaf(b0, m1, a1);
-        }
-        mulc[i][k] = f2_pack(m[0], m[1]);
-        addc[i][k] = f2_pack(a[0], a[1]);
+      for (int j = 0; j < 8; ++j) {
+        const int n = i * T * 8 + j;
+        const float w0 = w != nullptr ? w_t[n] : 1.f, b0 = (w != nullptr && b != nullptr) ? b_t[n] : 0.f;
+        const float m1 = scale != nullptr ? 1.f + sc_t[n] : 1.f, a1 = scale != nullptr ? sh_t[n] : 0.f;
+        m[j] = w0 * m1;
+        a[j] = fmaf(b0, m1, a1);
       }
+      if (i < CR) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          mulc[i < CR ? i : 0][k] = f2_pack(m[2 * k], m[2 * k + 1]);
+          addc[i < CR ? i : 0][k] = f2_pack(a[2 * k], a[2 * k + 1]);
+        }
+      } else {
+        // the other vectors' coefficients: shared memory, in the order this thread reads them back (no barrier)
+        coef[((i - CR) * 4 + 0) * T] = make_float4(m[0], m[1], m[2], m[3]);
+        coef[((i - CR) * 4 + 1) * T] = make_float4(m[4], m[5], m[6], m[7]);
+        coef[((i - CR) * 4 + 2) * T] = make_float4(a[0], a[1], a[2], a[3]);
+        coef[((i - CR) * 4 + 3) * T] = make_float4(a[4], a[5], a[6], a[7]);
+      }
+    }
   }
   int64_t t = blockIdx.x;
   const int64_t step = gridDim.x;
@@ -318,19 +328,11 @@ ln_rows_cta_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t D, int6
             v0 = f2_fma(v0, mulc[i < CR ? i : 0][2 * h], addc[i < CR ? i : 0][2 * h]);
             v1 = f2_fma(v1, mulc[i < CR ? i : 0][2 * h + 1], addc[i < CR ? i : 0][2 * h + 1]);
           }
-        } else {
-        if (w != nullptr) {
-          const float4 m = __ldg(reinterpret_cast<const float4*>(w_t + i * T * 8 + 4 * h));
-          const float4 a = b != nullptr ? __ldg(reinterpret_cast<const float4*>(b_t + i * T * 8 + 4 * h)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        } else if (affine) {
+          const float4 m = coef[((i - CR) * 4 + h) * T];
+          const float4 a = coef[((i - CR) * 4 + 2 + h) * T];
           v0 = f2_fma(v0, f2_pack(m.x, m.y), f2_pack(a.x, a.y));
           v1 = f2_fma(v1, f2_pack(m.z, m.w), f2_pack(a.z, a.w));
-        }
-        if (scale != nullptr) {
-          const float4 m = __ldg(reinterpret_cast<const float4*>(sc_t + i * T * 8 + 4 * h));
-          const float4 a = __ldg(reinterpret_cast<const float4*>(sh_t + i * T * 8 + 4 * h));
-          v0 = f2_fma(v0, f2_add(f2_pack(m.x, m.y), one2), f2_pack(a.x, a.y));
-          v1 = f2_fma(v1, f2_add(f2_pack(m.z, m.w), one2), f2_pack(a.z, a.w));
-        }
         }
         // the tensor the reference materialises in the activation dtype
         out[i].w[2 * h] = f2_to16_rn<BF16>(v0);
@@ -368,8 +370,10 @@ template <bool BF16, int QDT, int T, int NV, int MINB, int CR>
 int launch_cta_rows(int64_t s, cudaStream_t st, const uint16_t* x, int64_t D, int64_t ldx, const float* w, const float* b,
                     const float* shift, const float* scale, float eps, uint16_t* y, int64_t ldy, uint8_t* q, float* qscale) {
   int per_sm = 0;
-  constexpr size_t smem = static_cast<size_t>(kRing) * NV * T * sizeof(V8);
-  static_assert(smem <= 48 * 1024, "the ring fits the default dynamic shared memory limit");
+  constexpr size_t smem = static_cast<size_t>(kRing) * NV * T * sizeof(V8) + static_cast<size_t>(NV - CR) * 4 * T * sizeof(float4);
+  if (smem > 40 * 1024)
+    DAX_CUDA(cudaFuncSetAttribute(ln_rows_cta_kernel<BF16, QDT, T, NV, MINB, CR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(smem)));
   DAX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ln_rows_cta_kernel<BF16, QDT, T, NV, MINB, CR>, T, smem));
   const unsigned grid = static_cast<unsigned>(std::min<int64_t>(s, static_cast<int64_t>(sm_count()) * std::max(per_sm, 1)));
   ln_rows_cta_kernel<BF16, QDT, T, NV, MINB, CR><<<grid, T, smem, st>>>(x, s, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale);
@@ -403,7 +407,7 @@ int dispatch_nv(int64_t s, cudaStream_t st, const uint16_t* x, int64_t D, int64_
 #define DAX_LN_CTA(T, NV, MINB, CR) \
   if (D == 8 * (T) * (NV)) \
   return launch_cta_rows<BF16, QDT, T, NV, MINB, CR>(s, st, x, D, ldx, w, b, shift, scale, eps, y, ldy, q, qscale)
-  DAX_LN_CTA(160, 4, 3, 2);   // 5120
+  DAX_LN_CTA(160, 4, 4, 1);   // 5120
   DAX_LN_CTA(128, 4, 4, 2);   // 4096
   DAX_LN_CTA(128, 3, 5, 2);   // 3072
   DAX_LN_CTA(128, 2, 6, 2);   // 2048
