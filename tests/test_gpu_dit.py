@@ -63,6 +63,22 @@ def test_layernorm_modulate_quant_many_rows(ops):
         assert torch.equal(yi[0], y[i]) and torch.equal(qi[0], q[i]) and torch.equal(si[0], qs[i])
 
 
+@pytest.mark.parametrize("D", [256, 5120])
+def test_layernorm_strided_rows(ops, D):
+    """Rows that are a column slice of a wider matrix (leading dimension larger than the width): same results as the
+    contiguous copy, in both kernels."""
+    torch.manual_seed(11)
+    s = 300
+    wide = torch.randn(s, D + 64).bfloat16().to(DEV)
+    xs = wide[:, :D]
+    assert xs.stride(0) == D + 64
+    shift, scale = (0.2 * torch.randn(D)).to(DEV), (0.2 * torch.randn(D)).to(DEV)
+    for qd in (torch.int8, torch.float8_e4m3fn):
+        y0, q0, s0 = ops.layernorm_modulate_quant(xs.contiguous(), shift=shift, scale=scale, q_dtype=qd)
+        y1, q1, s1 = ops.layernorm_modulate_quant(xs, shift=shift, scale=scale, q_dtype=qd)
+        assert torch.equal(y0, y1) and torch.equal(q0, q1) and torch.equal(s0, s1)
+
+
 @pytest.mark.parametrize("D", [5120, 1000 * 8])
 def test_layernorm_rows_with_a_large_mean(ops, D):
     """Rows whose mean dwarfs their spread (E[x^2] - mean^2 would cancel) and a constant row: the centred form must

@@ -271,6 +271,24 @@ def test_rmsnorm_rope_pack(ops, dtype):
     assert O.rel_l2(y4.cpu(), O.rmsnorm(x, w)) <= 2e-3
 
 
+@pytest.mark.parametrize("H", [3, 40])
+def test_rmsnorm_rope_pack_strided_rows(ops, H):
+    """Input rows that are a column slice of a wider matrix (leading dimension larger than the width): same results as
+    the contiguous copy."""
+    torch.manual_seed(13)
+    grid = (2, 5, 9)
+    S, D = 90, H * 128
+    wide = torch.randn(S, D + 128).bfloat16().to(DEV)
+    xs = wide[:, :D]
+    w = (1 + 0.1 * torch.randn(D)).bfloat16().to(DEV)
+    fr = O.rope_table(grid)
+    cos = fr.real.float().reshape(S, 64).contiguous().to(DEV)
+    sin = fr.imag.float().reshape(S, 64).contiguous().to(DEV)
+    y0 = ops.rmsnorm_rope_pack(xs.contiguous(), norm_weight=w, do_norm=True, rope_cos=cos, rope_sin=sin)
+    y1 = ops.rmsnorm_rope_pack(xs, norm_weight=w, do_norm=True, rope_cos=cos, rope_sin=sin)
+    assert torch.equal(y0, y1)
+
+
 @pytest.mark.parametrize("H", [2, 16, 24, 32, 56, 64, 72])
 def test_rmsnorm_rope_pack_widths(ops, H):
     """One width per kernel variant: rows that fill the CTA exactly (no predicates) and ragged ones, 1 to 4 vectors
